@@ -15,6 +15,9 @@ behind the window of all further queries (``commit``).  The extra last page of
 each tensor is a sink for padded tokens of captured decode batches; it is
 never handed out.
 
+A mixer made of several mixers asks for a tuple of requirements; its entry's cache then
+has ``parts``, one per requirement (pages from the group of that requirement, a state of its own).
+
 Mixers with :class:`FixedState` get, per owning entry, a tensor
 ``[max_requests + 1, *shape]``; a request holds one slot index from admission
 to release, for all of them.  The slot is assigned even when no entry has
@@ -30,7 +33,7 @@ import torch
 
 import ctypes
 
-from ..parts.base import FixedState, PagedKV
+from ..parts.base import FixedState, PagedKV, requirement_parts
 from . import native
 from .pool import OutOfPages, PoolError, PoolView
 
@@ -45,6 +48,8 @@ class EntryCache:
     k: Optional[torch.Tensor] = None        # [pages + 1, kv_heads, page_size, head_dim]
     v: Optional[torch.Tensor] = None        # [pages + 1, kv_heads, head_dim, page_size]
     state: Optional[torch.Tensor] = None    # [max_requests + 1, *shape]
+    # an entry whose mixer is made of several mixers (kind "several"): what each of them sees, in the order it asked
+    parts: List["EntryCache"] = field(default_factory=list)
 
 
 @dataclass
@@ -101,11 +106,14 @@ class CacheManager:
         for i, req in enumerate(requirements):
             if cache_from[i] is not None:
                 continue
-            if isinstance(req, PagedKV):
-                if req not in by_key:
-                    by_key[req] = len(self.groups)
-                    self.groups.append(Group(req, [], None, None))
-                self.groups[by_key[req]].entries.append(i)
+            for part in requirement_parts(req):
+                if isinstance(part, PagedKV):
+                    if part not in by_key:
+                        by_key[part] = len(self.groups)
+                        self.groups.append(Group(part, [], None, None))
+                    if i in self.groups[by_key[part]].entries:
+                        raise ValueError(f"schedule entry {i} asks twice for the same paged cache {part!r}")
+                    self.groups[by_key[part]].entries.append(i)
         if self.num_pages <= 0 or self.max_requests <= 0:
             raise ValueError("a cache needs at least one page and one request slot")
         # pools, block tables and the step packer live in the host runtime (csrc/host/runtime.cpp)
@@ -123,26 +131,33 @@ class CacheManager:
                 g.tables = torch.full((self.max_requests + 1, self.table_blocks), self.num_pages, dtype=torch.int32, device=self.device)
                 g.kv = torch.zeros((len(g.entries), 2, self.num_pages + 1, g.key.num_kv_heads, self.page_size * g.key.head_dim),
                                    dtype=dtype, device=self.device)
-        for i, req in enumerate(requirements):
-            src = cache_from[i]
-            if src is not None:
-                owner = self.entries[src]
-                self.entries.append(EntryCache(owner.kind, False, owner.group, owner.k, owner.v, owner.state))
-            elif isinstance(req, PagedKV):
+        def single(i, req) -> EntryCache:
+            if isinstance(req, PagedKV):
                 gid = by_key[req]
                 g = self.groups[gid]
                 j = g.entries.index(i)
                 shape = (self.num_pages + 1, g.key.num_kv_heads)
                 k = g.kv[j, 0].view(*shape, self.page_size, g.key.head_dim) if g.kv is not None else None
                 v = g.kv[j, 1].view(*shape, g.key.head_dim, self.page_size) if g.kv is not None else None
-                self.entries.append(EntryCache("paged", True, gid, k, v))
-            elif isinstance(req, FixedState):
+                return EntryCache("paged", True, gid, k, v)
+            if isinstance(req, FixedState):
                 st = torch.zeros((self.max_requests + 1,) + tuple(req.shape), dtype=req.dtype, device=self.device) if allocate else None
-                self.entries.append(EntryCache("state", True, state=st))
+                return EntryCache("state", True, state=st)
+            raise TypeError(f"schedule entry {i}: unknown cache requirement {req!r}")
+
+        def reader(owner: EntryCache) -> EntryCache:
+            return EntryCache(owner.kind, False, owner.group, owner.k, owner.v, owner.state, [reader(p) for p in owner.parts])
+
+        for i, req in enumerate(requirements):
+            src = cache_from[i]
+            if src is not None:
+                self.entries.append(reader(self.entries[src]))
             elif req is None:
                 self.entries.append(EntryCache("none"))
+            elif isinstance(req, (tuple, list)):
+                self.entries.append(EntryCache("several", True, parts=[single(i, r) for r in requirement_parts(req)]))
             else:
-                raise TypeError(f"schedule entry {i}: unknown cache requirement {req!r}")
+                self.entries.append(single(i, req))
 
     # ------------------------------------------------------------------
     @property
@@ -173,18 +188,21 @@ class CacheManager:
     def admit(self, request_id: int) -> RequestCache:
         slot = ctypes.c_int(0)
         native.check(self._lib.li_cm_admit(self._h, int(request_id), ctypes.byref(slot)))
-        for e in self.entries:
-            if e.kind == "state" and e.writes and e.state is not None:
-                e.state[slot.value].zero_()
+        self._clear_states(slot.value)
         rc = RequestCache(int(request_id), slot.value, self)
         self.live[rc.request_id] = rc
         return rc
 
+    def _clear_states(self, slot: int) -> None:
+        """A request starts from a state of zeros in every entry that keeps one."""
+        for e in self.entries:
+            for c in [e] + e.parts:
+                if c.kind == "state" and c.writes and c.state is not None:
+                    c.state[slot].zero_()
+
     def adopt(self, request_id: int, slot: int) -> RequestCache:
         """The host runtime admitted a request by itself (its scheduler does): the picture of it here."""
-        for e in self.entries:
-            if e.kind == "state" and e.writes and e.state is not None:
-                e.state[slot].zero_()
+        self._clear_states(int(slot))
         rc = RequestCache(int(request_id), int(slot), self)
         self.live[rc.request_id] = rc
         return rc

@@ -1,3 +1,4 @@
+from .filasun import FilasunConfig
 from .qwen2 import ConfigError, Qwen2Config
 from .registry import (
     config_class_for,
@@ -12,6 +13,7 @@ from .spec import BlockSpec, ModelSpec, PartSpec, ScheduleEntry, default_schedul
 __all__ = [
     "BlockSpec",
     "ConfigError",
+    "FilasunConfig",
     "ModelSpec",
     "PartSpec",
     "Qwen2Config",

@@ -13,6 +13,7 @@ import json
 from pathlib import Path
 from typing import Any, Dict, Mapping, Type
 
+from .filasun import FilasunConfig
 from .qwen2 import ConfigError, Qwen2Config
 from .spec import ModelSpec
 
@@ -41,10 +42,10 @@ def config_class_for(name: str) -> Type:
 
 
 def config_from_dict(d: Mapping[str, Any]):
-    archs = d.get("architectures")
+    archs = d.get("architectures") or d.get("architecture")        # a list of names (the first counts), or one name
     if not archs:
         raise ConfigError("config.json: missing key 'architectures'")
-    return config_class_for(archs[0]).from_dict(d)
+    return config_class_for(archs if isinstance(archs, str) else archs[0]).from_dict(d)
 
 
 def load_config(model_dir):
@@ -61,3 +62,4 @@ def model_spec_from_dir(model_dir) -> ModelSpec:
 
 
 register_architecture(Qwen2Config.ARCHITECTURE, Qwen2Config)
+register_architecture(FilasunConfig.ARCHITECTURE, FilasunConfig)

@@ -125,6 +125,9 @@ class ModelSpec:
     # factor on the embedding rows and cap of the logits (cap * tanh(logits / cap)); None: neither
     embedding_scale: Optional[float] = None
     logit_cap: Optional[float] = None
+    # the residual stream is kept as this many streams (hyper-connections): copies of the embedding at the start, their
+    # sum at the end; every block then is of an arrangement that takes them
+    streams: int = 1
     # other names under which a declared tensor may be stored: declared name -> names tried after it
     aliases: Mapping[str, Tuple[str, ...]] = field(default_factory=dict)
 

@@ -16,6 +16,11 @@
 // Cache layout: keys [page][kv_head][offset][head_dim], values transposed
 // [page][kv_head][head_dim][offset]; the page of key t of sequence s is
 // block_table[s][t / page_size].  Any head_dim up to 512.
+//
+// Optional changes of the scores and the output (all off when zero / null):
+//   softcap > 0:  s <- softcap * tanh(s / softcap) after the scale;
+//   slopes [nh]:  s <- s - slopes[h] * (p - key), a penalty linear in the distance;
+//   gate [T, nh]: the head's output is multiplied by 1 / (1 + exp(-gate[t, h])).
 #include "common.cuh"
 
 namespace {
@@ -28,7 +33,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_of_token,
                          const int* __restrict__ positions, int total, int nh, int nkv, int dh, int page_size, int num_pages,
-                         float scale, int window) {
+                         float scale, int window, float softcap, const float* __restrict__ slopes, const T* __restrict__ gate) {
     const int warp = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (warp >= total) return;
@@ -49,6 +54,7 @@ attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, const T
         acc[i] = 0.0f;
     }
     float m = -INFINITY, l = 0.0f;
+    const float slope = slopes ? slopes[h] : 0.0f;
     const int* bt = block_table + (size_t)s * max_blocks;
     for (int key = lo; key <= p; ++key) {
         const int lb = key / page_size;
@@ -63,7 +69,9 @@ attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, const T
             const int d = lane + 32 * i;
             if (i < per && d < dh) dot = fmaf(qr[i], to_float(kcache[base + d]), dot);
         }
-        const float sc = warp_sum(dot) * scale;
+        float sc = warp_sum(dot) * scale;
+        if (softcap > 0.0f) sc = softcap * tanhf(sc / softcap);
+        sc -= slope * (float)(p - key);
         const float mn = fmaxf(m, sc);
         const float alpha = expf(m - mn);
         const float e = expf(sc - mn);
@@ -76,7 +84,8 @@ attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, const T
         m = mn;
     }
     T* o = out + (size_t)t * nh * dh + h * dh;
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    if (gate) inv *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * nh + h])));
 #pragma unroll
     for (int i = 0; i < kMaxPerLane; ++i) {
         const int d = lane + 32 * i;
@@ -88,7 +97,8 @@ attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, const T
 
 int li_attention_generic(const void* qkv, void* out, const void* kcache, const void* vcache, int dtype, const int* block_table,
                          int max_blocks, const int* seq_of_token, const int* positions, int T, int nh, int nkv, int dh,
-                         int page_size, int num_pages, float scale, int window, cudaStream_t stream) {
+                         int page_size, int num_pages, float scale, int window, float softcap, const float* slopes, const void* gate,
+                         cudaStream_t stream) {
     LI_REQUIRE(dh <= 32 * kMaxPerLane, "attention: head_dim %d is larger than %d", dh, 32 * kMaxPerLane);
     const long long total = (long long)T * nh;
     LI_REQUIRE(total < (1LL << 31), "attention: too many (token, head) pairs");
@@ -96,11 +106,11 @@ int li_attention_generic(const void* qkv, void* out, const void* kcache, const v
     if (dtype == LI_F32)
         attention_generic_kernel<float><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
             (const float*)qkv, (float*)out, (const float*)kcache, (const float*)vcache, block_table, max_blocks, seq_of_token, positions,
-            (int)total, nh, nkv, dh, page_size, num_pages, scale, window);
+            (int)total, nh, nkv, dh, page_size, num_pages, scale, window, softcap, slopes, (const float*)gate);
     else if (dtype == LI_BF16)
         attention_generic_kernel<bf16><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
             (const bf16*)qkv, (bf16*)out, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks, seq_of_token, positions,
-            (int)total, nh, nkv, dh, page_size, num_pages, scale, window);
+            (int)total, nh, nkv, dh, page_size, num_pages, scale, window, softcap, slopes, (const bf16*)gate);
     else
         return li_fail("attention: unknown dtype %d", dtype);
     return li_check_launch("attention (generic)");

@@ -302,6 +302,61 @@ LI_EXPORT int li_swiglu(const void* gate_up, void* out, int dtype, int T, int I,
     return li_check_launch("swiglu");
 }
 
+// out = sa * a + sb * b over n elements of the run dtype, the sum in float.
+namespace {
+template <typename T>
+__global__ void weighted_sum2_kernel(const T* __restrict__ a, const T* __restrict__ b, float sa, float sb, T* __restrict__ out, long long n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) out[i] = from_float<T>(fmaf(sa, to_float(a[i]), sb * to_float(b[i])));
+}
+}  // namespace
+
+LI_EXPORT int li_weighted_sum2(const void* a, const void* b, float sa, float sb, void* out, int dtype, long long n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    if (dtype == LI_F32)
+        weighted_sum2_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)a, (const float*)b, sa, sb, (float*)out, n);
+    else if (dtype == LI_BF16)
+        weighted_sum2_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)a, (const bf16*)b, sa, sb, (bf16*)out, n);
+    else
+        return li_fail("weighted_sum2: unknown dtype %d", dtype);
+    return li_check_launch("weighted_sum2");
+}
+
+// A gated unit with bounded operands: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g / (1 + exp(-alpha g)) * (u + 1); gate_up [T, 2 I] as gate | up.  Float arithmetic, one rounding.
+namespace {
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, long long n, float limit, float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        const long long t = i / I;
+        const int j = (int)(i - t * I);
+        const float g = fminf(to_float(gate_up[t * 2 * I + j]), limit);
+        const float u = fminf(fmaxf(to_float(gate_up[t * 2 * I + I + j]), -limit), limit);
+        out[i] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    }
+}
+}  // namespace
+
+LI_EXPORT int li_glu_clamped(const void* gate_up, void* out, int dtype, int T, int I, float limit, float alpha, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && I > 0, "glu_clamped: bad sizes T=%d I=%d", T, I);
+    const long long n = (long long)T * I;
+    if (n == 0) return 0;
+    if (dtype == LI_F32)
+        glu_clamped_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, I, n, limit, alpha);
+    else if (dtype == LI_BF16)
+        glu_clamped_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, n, limit, alpha);
+    else
+        return li_fail("glu_clamped: unknown dtype %d", dtype);
+    return li_check_launch("glu_clamped");
+}
+
 // out[tok, :] = hprime[tok, :] / sqrt(sum of ssq[:, tok] / width + eps): the normalised activation itself, for a
 // consumer that cannot take the factor into its own product (row_scale.cuh).  bfloat16.
 namespace {

@@ -36,12 +36,14 @@ int li_table_gather(int* resident, int rows, int cols, const int* updates, int u
  * through block_table[s]; singles: how many sequences of a step with longer portions have one token (negative: not
  * known); units (may be NULL): the work list of the kernel for long portions, made with the step's metadata (two counts,
  * two unused words, then per entry: sequence, tile of 128 tokens, part | parts << 8, unused), with the number of entries
- * to launch when the single tokens go to the decode kernel and when they do not. */
+ * to launch when the single tokens go to the decode kernel and when they do not.  softcap > 0: scores become
+ * softcap * tanh(score / softcap); slopes [nh] (may be NULL): slopes[h] * (p - key) is taken off the score of head h;
+ * gate [T, nh] in the run dtype (may be NULL): head h's output is multiplied by 1 / (1 + exp(-gate[t, h])). */
 int li_paged_attention(const void* qkv, void* out, const void* kcache, const void* vcache, int dtype, const int*
     block_table, int max_blocks, const int* q_start, const int* ctx_lens, const int* seq_of_token, const int*
     positions, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window, int
     max_q_len, int max_ctx_len, const int* old_lens, int singles, const int* units, int slots_portions, int slots_all,
-    cudaStream_t stream);
+    float softcap, const float* slopes, const void* gate, cudaStream_t stream);
 
 /* The same through one implementation: 0 general, 1 decode, 2 mma.sync tiles, 3 tcgen05 tiles (tests and
  * measurements). */
@@ -49,7 +51,7 @@ int li_paged_attention_with(int which, const void* qkv, void* out, const void* k
     const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens, const int* seq_of_token, const
     int* positions, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window, int
     max_q_len, int max_ctx_len, const int* old_lens, int singles, const int* units, int slots_portions, int slots_all,
-    cudaStream_t stream);
+    float softcap, const float* slopes, const void* gate, cudaStream_t stream);
 
 /* ---- decode_step.cu: a decode step as one persistent kernel (decode_step.h has the structures) ---- */
 struct LiDecodeStep;
@@ -92,6 +94,58 @@ int li_swiglu(const void* gate_up, void* out, int dtype, int T, int I, cudaStrea
  * products, applied on its own). */
 int li_apply_row_scale(const void* hprime, const float* ssq, int nparts, int width, float eps, void* out, int M, int
     H, cudaStream_t stream);
+
+/* out[t, i] = g / (1 + exp(-alpha g)) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); gate_up
+ * [T, 2 I] as gate | up. */
+int li_glu_clamped(const void* gate_up, void* out, int dtype, int T, int I, float limit, float alpha, cudaStream_t stream);
+
+/* out = sa a + sb b over n elements of the run dtype (the sum in float). */
+int li_weighted_sum2(const void* a, const void* b, float sa, float sb, void* out, int dtype, long long n, cudaStream_t stream);
+
+/* ---- hyper.cu: the residual stream as s parallel streams xs [T, s, H] (float) ---- */
+/* out[r] = RMSNorm(sum_s in_w[s] xs[rows[r], s]) * w; in_w NULL: the plain sum; rows NULL: every row in order. */
+int li_hc_read_norm(const float* xs, const float* in_w, const int* rows, const float* w, float eps, void* out, int dtype, int R,
+    int T, int s, int H, cudaStream_t stream);
+
+/* xs[t, r] = sum_s mix[s, r] xs[t, s] + out_w[r] y[t] (all streams from the old ones); then, unless next_out is NULL,
+ * next_out[t] = RMSNorm(sum_r next_in[r] xs[t, r]) * next_w. */
+int li_hc_update(float* xs, const void* y, int dtype, const float* mix, const float* out_w, const float* next_in, const float* next_w,
+    float eps, void* next_out, int T, int s, int H, cudaStream_t stream);
+
+/* xs[t, a] = x[t] for every stream a. */
+int li_hc_expand(const float* x, float* xs, int T, int s, int H, cudaStream_t stream);
+
+/* x[t] += table[positions[t]]: learned absolute positions, table [P, H] in the run dtype. */
+int li_add_position_rows(float* x, const void* table, int dtype, const int* positions, int T, int H, int P, cudaStream_t stream);
+
+/* ---- recurrent.cu: mixers with a state of fixed size per request (state [slots, state_stride] float) ---- */
+/* out[t, c] = silu(b[c] + sum_k w[c, k] in_(t - taps + 1 + k)[c]) over the C channels at column in_off of in [T,
+ * in_stride]; inputs before a sequence's portion come from its state (the last taps - 1 inputs, oldest first, at
+ * state_off). */
+int li_causal_conv_silu(const void* in, int dtype, int in_stride, int in_off, const float* w, const float* b, const float* state,
+    long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
+    void* out, int T, int C, int taps, cudaStream_t stream);
+
+/* Moves every sequence's convolution state on by its portion (after li_causal_conv_silu has read it). */
+int li_conv_state_shift(const void* in, int dtype, int in_stride, int in_off, float* state, long long state_stride, long long state_off,
+    const int* q_start, const int* slots, int S, int C, int taps, cudaStream_t stream);
+
+/* Per head S [N, P]: S = exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x, dt = softplus(dt_raw + dt_bias); xbc
+ * [T, C] holds x | B | C; a sequence's tokens in order, its state read and written once. */
+int li_ssm_scan(const void* xbc, int dtype, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log,
+    const float* D, float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads,
+    int P, int N, int groups, cudaStream_t stream);
+
+/* Per head S [d, dv]: S = decay S + k v^T, out = S^T q, with q, k, v = silu of the columns at q_off, k_off, v_off
+ * of qkv [T, stride]. */
+int li_decay_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const float* decay, float* state,
+    long long state_stride, const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv,
+    cudaStream_t stream);
+
+/* RMSNorm of y [T, n] (float) in `groups` equal parts, times w; mode 0: y is first multiplied by silu(gate), mode 1:
+ * the result is multiplied by sigmoid(gate); gate [T, gate_stride] at column gate_off, in the run dtype like out. */
+int li_gated_rmsnorm(const float* y, const void* gate, int dtype, int gate_stride, int gate_off, const float* w, float eps, int mode,
+    void* out, int T, int n, int groups, cudaStream_t stream);
 
 /* ---- gemm_tcgen05.cu ---- */
 /* Measurements: 0 keeps the rotary epilogue to paired tiles. */

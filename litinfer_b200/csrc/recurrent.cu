@@ -1,0 +1,306 @@
+// Mixers that carry a state of fixed size per request instead of a cache that grows: the plain kernels.
+//
+// Every kernel here finds a sequence's tokens through q_start[s] .. q_start[s + 1] and its state through
+// state_slots[s], both on the device, so a step of single tokens launches the same grid whatever the slots hold and can
+// be replayed from a captured graph.  A sequence's tokens are walked in order inside one block; the state is read once,
+// kept in shared memory and written once.  State, decays, step sizes, gates of the recurrence and every sum are float;
+// the projections come in the run dtype.
+//
+//   * li_causal_conv_silu / li_conv_state_shift: a depthwise causal convolution over the last `taps` inputs of each
+//     channel followed by x / (1 + exp(-x)); the taps - 1 inputs before a portion come from the state, which the
+//     second kernel then moves on (two launches: every token of the step reads the old state).
+//   * li_ssm_scan: per head a state S [N, P]:  S = exp(-exp(A_log) dt) S + dt B x^T,  y = S^T C + D x, with
+//     dt = softplus(dt_raw + dt_bias) per token and head, B and C shared by the heads of a group.
+//   * li_decay_scan: per head a state S [d, dv]:  S = decay S + k v^T,  o = S^T q, with q, k, v passed through
+//     x / (1 + exp(-x)) on the way in.
+//   * li_gated_rmsnorm: RMSNorm in equal groups of a float row, with a gate before the norm (y * silu(z)) or after
+//     it (norm(y) * sigmoid(g)).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); }
+
+constexpr int kMaxTaps = 8;
+
+// in: [T, in_stride] with the C channels at column in_off; w [C, taps] (the last tap is the current token's), b [C];
+// state [slots, state_stride] with the last taps - 1 inputs at state_off, oldest first, [taps - 1, C].
+template <typename T>
+__global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride, int in_off, const float* __restrict__ w, const float* __restrict__ b,
+                                        const float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ q_start,
+                                        const int* __restrict__ seq_of_token, const int* __restrict__ slots, T* __restrict__ out, int C, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int s = seq_of_token[t];
+    const int q0 = q_start[s];
+    const int li = t - q0;
+    const float* st = state + (size_t)slots[s] * state_stride + state_off;
+    float acc = b[c];
+    for (int k = 0; k < taps; ++k) {
+        const int i = li - (taps - 1) + k;
+        const float v = i >= 0 ? to_float(in[(size_t)(q0 + i) * in_stride + in_off + c]) : st[(size_t)(taps - 1 + i) * C + c];
+        acc = fmaf(w[(size_t)c * taps + k], v, acc);
+    }
+    out[(size_t)t * C + c] = from_float<T>(silu_f(acc));
+}
+
+template <typename T>
+__global__ void conv_state_shift_kernel(const T* __restrict__ in, int in_stride, int in_off, float* __restrict__ state, long long state_stride,
+                                        long long state_off, const int* __restrict__ q_start, const int* __restrict__ slots, int C, int taps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int q0 = q_start[s], n = q_start[s + 1] - q0;
+    if (n <= 0) return;
+    float* st = state + (size_t)slots[s] * state_stride + state_off;
+    float keep[kMaxTaps];
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j) {
+        if (j < taps - 1) {
+            const int i = n - (taps - 1) + j;                    // index among the portion's inputs; negative: an older one
+            keep[j] = i >= 0 ? to_float(in[(size_t)(q0 + i) * in_stride + in_off + c]) : st[(size_t)(taps - 1 + i) * C + c];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j)
+        if (j < taps - 1) st[(size_t)j * C + c] = keep[j];
+}
+
+// One block per (head, sequence), a thread per column of the head's state.
+// xbc [T, C]: x (heads * P) | B (groups * N) | C (groups * N), after convolution and activation.
+template <typename T>
+__global__ void ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, int dt_stride, const float* __restrict__ dt_bias,
+                                const float* __restrict__ A_log, const float* __restrict__ D, float* __restrict__ state, long long state_stride,
+                                const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ y, int heads, int P, int N,
+                                int groups) {
+    extern __shared__ float smem[];
+    float* S = smem;                       // [N][P]
+    float* bc = smem + (size_t)N * P;      // two buffers of B [N] | C [N]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.x, s = blockIdx.y, c = threadIdx.x;
+    const int q0 = q_start[s], q1 = q_start[s + 1];
+    if (q1 <= q0) return;
+    const int g = h / (heads / groups);
+    const int inner = heads * P;
+    float* st = state + (size_t)slots[s] * state_stride + (size_t)h * N * P;
+    for (int i = c; i < N * P; i += blockDim.x) S[i] = st[i];
+    const float rate = expf(A_log[h]), bias = dt_bias[h], skip = D[h];
+    for (int t = q0; t < q1; ++t) {
+        float* buf = bc + (size_t)((t - q0) & 1) * 2 * N;
+        const T* row = xbc + (size_t)t * C;
+        for (int n = c; n < N; n += blockDim.x) {
+            buf[n] = to_float(row[inner + g * N + n]);
+            buf[N + n] = to_float(row[inner + (groups + g) * N + n]);
+        }
+        __syncthreads();
+        if (c < P) {
+            const float dt = softplus_f(to_float(dt_raw[(size_t)t * dt_stride + h]) + bias);
+            const float decay = expf(-rate * dt);
+            const float x = to_float(row[h * P + c]);
+            const float dx = dt * x;
+            float acc = 0.0f;
+            for (int n = 0; n < N; ++n) {
+                const float v = fmaf(decay, S[n * P + c], buf[n] * dx);
+                S[n * P + c] = v;
+                acc = fmaf(v, buf[N + n], acc);
+            }
+            y[(size_t)t * inner + h * P + c] = fmaf(skip, x, acc);
+        }
+    }
+    __syncthreads();
+    for (int i = c; i < N * P; i += blockDim.x) st[i] = S[i];
+}
+
+// One block per (head, sequence), a thread per column of the head's state.
+// q, k [T, stride] at columns q_off + h d, k_off + h d; v at v_off + h dv; all before their activation.
+template <typename T>
+__global__ void decay_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int v_off, const float* __restrict__ decay,
+                                  float* __restrict__ state, long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots,
+                                  float* __restrict__ out, int heads, int d, int dv) {
+    extern __shared__ float smem[];
+    float* S = smem;                       // [d][dv]
+    float* qk = smem + (size_t)d * dv;     // two buffers of q [d] | k [d]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.x, s = blockIdx.y, c = threadIdx.x;
+    const int q0 = q_start[s], q1 = q_start[s + 1];
+    if (q1 <= q0) return;
+    float* st = state + (size_t)slots[s] * state_stride + (size_t)h * d * dv;
+    for (int i = c; i < d * dv; i += blockDim.x) S[i] = st[i];
+    const float lam = decay[h];
+    for (int t = q0; t < q1; ++t) {
+        float* buf = qk + (size_t)((t - q0) & 1) * 2 * d;
+        const T* row = qkv + (size_t)t * stride;
+        for (int i = c; i < d; i += blockDim.x) {
+            buf[i] = silu_f(to_float(row[q_off + h * d + i]));
+            buf[d + i] = silu_f(to_float(row[k_off + h * d + i]));
+        }
+        __syncthreads();
+        if (c < dv) {
+            const float v = silu_f(to_float(row[v_off + h * dv + c]));
+            float acc = 0.0f;
+            for (int i = 0; i < d; ++i) {
+                const float sv = fmaf(lam, S[i * dv + c], buf[d + i] * v);
+                S[i * dv + c] = sv;
+                acc = fmaf(sv, buf[i], acc);
+            }
+            out[(size_t)t * heads * dv + h * dv + c] = acc;
+        }
+    }
+    __syncthreads();
+    for (int i = c; i < d * dv; i += blockDim.x) st[i] = S[i];
+}
+
+// One block per (token, group).  mode 0: v = y silu(z), out = v rinv w; mode 1: out = y rinv w sigmoid(z).
+template <typename T>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride, int gate_off, const float* __restrict__ w,
+                                     float eps, int mode, T* __restrict__ out, int n, int groups) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x / groups, g = blockIdx.x - t * groups;
+    const int gs = n / groups;
+    const float* yr = y + (size_t)t * n + (size_t)g * gs;
+    const T* zr = gate + (size_t)t * gate_stride + gate_off + (size_t)g * gs;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < gs; j += blockDim.x) {
+        float v = yr[j];
+        if (mode == 0) v *= silu_f(to_float(zr[j]));
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)gs + eps);
+    T* o = out + (size_t)t * n + (size_t)g * gs;
+    for (int j = threadIdx.x; j < gs; j += blockDim.x) {
+        float v = yr[j];
+        const float z = to_float(zr[j]);
+        if (mode == 0) v = (v * silu_f(z)) * rinv * w[g * gs + j];
+        else v = (v * rinv * w[g * gs + j]) * sigmoid_f(z);
+        o[j] = from_float<T>(v);
+    }
+}
+
+int round_up_warp(int n) { return (n + 31) / 32 * 32; }
+
+}  // namespace
+
+LI_EXPORT int li_causal_conv_silu(const void* in, int dtype, int in_stride, int in_off, const float* w, const float* b, const float* state,
+                                  long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
+                                  void* out, int T, int C, int taps, cudaStream_t stream) {
+    LI_REQUIRE(taps >= 1 && taps <= kMaxTaps, "causal convolution: %d taps (1..%d)", taps, kMaxTaps);
+    LI_REQUIRE(C > 0 && in_off >= 0 && in_off + C <= in_stride, "causal convolution: %d channels at column %d of %d", C, in_off, in_stride);
+    if (T == 0) return 0;
+    LI_REQUIRE(T <= 65535, "causal convolution: %d tokens in one launch", T);
+    const dim3 grid(ceil_div(C, 128), T);
+    cudaError_t e;
+    if (dtype == LI_F32)
+        e = li_launch_pdl(causal_conv_silu_kernel<float>, grid, dim3(128), 0, stream, (const float*)in, in_stride, in_off, w, b, state, state_stride,
+                          state_off, q_start, seq_of_token, slots, (float*)out, C, taps);
+    else if (dtype == LI_BF16)
+        e = li_launch_pdl(causal_conv_silu_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)in, in_stride, in_off, w, b, state, state_stride,
+                          state_off, q_start, seq_of_token, slots, (bf16*)out, C, taps);
+    else
+        return li_fail("causal convolution: unknown dtype %d", dtype);
+    if (e != cudaSuccess) return li_fail("causal convolution: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("causal_conv_silu");
+}
+
+LI_EXPORT int li_conv_state_shift(const void* in, int dtype, int in_stride, int in_off, float* state, long long state_stride, long long state_off,
+                                  const int* q_start, const int* slots, int S, int C, int taps, cudaStream_t stream) {
+    LI_REQUIRE(taps >= 1 && taps <= kMaxTaps, "causal convolution: %d taps (1..%d)", taps, kMaxTaps);
+    if (S == 0 || taps == 1) return 0;
+    LI_REQUIRE(S <= 65535, "causal convolution: %d sequences in one launch", S);
+    const dim3 grid(ceil_div(C, 128), S);
+    cudaError_t e;
+    if (dtype == LI_F32)
+        e = li_launch_pdl(conv_state_shift_kernel<float>, grid, dim3(128), 0, stream, (const float*)in, in_stride, in_off, state, state_stride, state_off,
+                          q_start, slots, C, taps);
+    else if (dtype == LI_BF16)
+        e = li_launch_pdl(conv_state_shift_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)in, in_stride, in_off, state, state_stride, state_off,
+                          q_start, slots, C, taps);
+    else
+        return li_fail("causal convolution: unknown dtype %d", dtype);
+    if (e != cudaSuccess) return li_fail("conv_state_shift: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("conv_state_shift");
+}
+
+LI_EXPORT int li_ssm_scan(const void* xbc, int dtype, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log,
+                          const float* D, float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads,
+                          int P, int N, int groups, cudaStream_t stream) {
+    LI_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0, "state-space scan: %d heads in %d groups", heads, groups);
+    LI_REQUIRE(P > 0 && P <= 1024 && N > 0, "state-space scan: head size %d, state size %d", P, N);
+    LI_REQUIRE(C == heads * P + 2 * groups * N, "state-space scan: %d channels for %d heads of %d and %d groups of %d", C, heads, P, groups, N);
+    if (S == 0) return 0;
+    LI_REQUIRE(S <= 65535, "state-space scan: %d sequences in one launch", S);
+    const size_t smem = ((size_t)N * P + 4 * (size_t)N) * sizeof(float);
+    LI_REQUIRE(smem <= 200 * 1024, "state-space scan: a state of %d x %d does not fit shared memory", N, P);
+    const dim3 grid(heads, S), block(round_up_warp(P));
+    cudaError_t e;
+    if (dtype == LI_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = li_launch_pdl(ssm_scan_kernel<float>, grid, block, smem, stream, (const float*)xbc, C, (const float*)dt_raw, dt_stride, dt_bias, A_log, D, state,
+                          state_stride, q_start, slots, y, heads, P, N, groups);
+    } else if (dtype == LI_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = li_launch_pdl(ssm_scan_kernel<bf16>, grid, block, smem, stream, (const bf16*)xbc, C, (const bf16*)dt_raw, dt_stride, dt_bias, A_log, D, state,
+                          state_stride, q_start, slots, y, heads, P, N, groups);
+    } else {
+        return li_fail("state-space scan: unknown dtype %d", dtype);
+    }
+    if (e != cudaSuccess) return li_fail("ssm_scan: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("ssm_scan");
+}
+
+LI_EXPORT int li_decay_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const float* decay, float* state,
+                            long long state_stride, const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv,
+                            cudaStream_t stream) {
+    LI_REQUIRE(heads > 0 && d > 0 && dv > 0 && dv <= 1024, "decay scan: %d heads of %d x %d", heads, d, dv);
+    if (S == 0) return 0;
+    LI_REQUIRE(S <= 65535, "decay scan: %d sequences in one launch", S);
+    const size_t smem = ((size_t)d * dv + 4 * (size_t)d) * sizeof(float);
+    LI_REQUIRE(smem <= 200 * 1024, "decay scan: a state of %d x %d does not fit shared memory", d, dv);
+    const dim3 grid(heads, S), block(round_up_warp(dv));
+    cudaError_t e;
+    if (dtype == LI_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = li_launch_pdl(decay_scan_kernel<float>, grid, block, smem, stream, (const float*)qkv, stride, q_off, k_off, v_off, decay, state, state_stride,
+                          q_start, slots, out, heads, d, dv);
+    } else if (dtype == LI_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = li_launch_pdl(decay_scan_kernel<bf16>, grid, block, smem, stream, (const bf16*)qkv, stride, q_off, k_off, v_off, decay, state, state_stride,
+                          q_start, slots, out, heads, d, dv);
+    } else {
+        return li_fail("decay scan: unknown dtype %d", dtype);
+    }
+    if (e != cudaSuccess) return li_fail("decay_scan: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("decay_scan");
+}
+
+LI_EXPORT int li_gated_rmsnorm(const float* y, const void* gate, int dtype, int gate_stride, int gate_off, const float* w, float eps, int mode,
+                               void* out, int T, int n, int groups, cudaStream_t stream) {
+    LI_REQUIRE(n > 0 && groups > 0 && n % groups == 0, "gated norm: %d columns in %d groups", n, groups);
+    LI_REQUIRE(mode == 0 || mode == 1, "gated norm: unknown mode %d", mode);
+    LI_REQUIRE(gate_off >= 0 && gate_off + n <= gate_stride, "gated norm: gate at column %d of %d for %d columns", gate_off, gate_stride, n);
+    if (T == 0) return 0;
+    const long long blocks = (long long)T * groups;
+    LI_REQUIRE(blocks < (1LL << 31), "gated norm: too many rows");
+    cudaError_t e;
+    if (dtype == LI_F32)
+        e = li_launch_pdl(gated_rmsnorm_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, y, (const float*)gate, gate_stride, gate_off, w, eps,
+                          mode, (float*)out, n, groups);
+    else if (dtype == LI_BF16)
+        e = li_launch_pdl(gated_rmsnorm_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, stream, y, (const bf16*)gate, gate_stride, gate_off, w, eps,
+                          mode, (bf16*)out, n, groups);
+    else
+        return li_fail("gated norm: unknown dtype %d", dtype);
+    if (e != cudaSuccess) return li_fail("gated_rmsnorm: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("gated_rmsnorm");
+}

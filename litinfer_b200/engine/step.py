@@ -28,7 +28,7 @@ import torch
 from ..cache import native
 from ..cache.manager import CacheManager
 from ..models.decoder import DecoderModel
-from ..parts.base import FixedState, Mixer
+from ..parts.base import FixedState, Mixer, has_fixed_state
 from .batch import StepContext, StepItem, context_from, pack_step, split_into_tokens
 
 
@@ -78,10 +78,10 @@ class ModelRunner:
         # a mixer with state of its own takes a request's tokens in order and advances its state every time the step
         # runs: its portions are never split, and nothing of such a model is captured (capturing runs the step for
         # warm-up, and a captured step would freeze which slots it updates) ...
-        self._may_split = not any(isinstance(r, FixedState) for r in model.cache_requirements())
+        self._may_split = not any(has_fixed_state(r) for r in model.cache_requirements())
 
         def mixers_with_state(part):
-            if isinstance(part, Mixer) and isinstance(part.cache_requirement(), FixedState):
+            if isinstance(part, Mixer) and isinstance(part.cache_requirement(), FixedState):          # (a mixer of mixers: its parts answer)
                 yield part
             for child in part.parts():
                 yield from mixers_with_state(child)

@@ -401,7 +401,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
                     max_q_len: int, max_ctx_len: int, implementation: Optional[str] = None,
                     old_lens: Optional[torch.Tensor] = None, singles: int = 0,
-                    units: Optional[torch.Tensor] = None, unit_slots: Tuple[int, int] = (0, 0)) -> None:
+                    units: Optional[torch.Tensor] = None, unit_slots: Tuple[int, int] = (0, 0),
+                    softcap: float = 0.0, slopes: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
     """Causal grouped-query attention of the step's tokens over the paged cache.
 
     Queries are the first ``num_heads * head_dim`` columns of ``qkv`` (already
@@ -414,7 +415,10 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     ``singles``: how many sequences of a step with longer portions have one token (negative: not known).  They then
     go to the decode kernel, the rest to the kernel for portions (bfloat16).
     ``units`` (int32, from ``engine.batch.attention_units``): the work list of the kernel for long portions, with
-    ``unit_slots`` = how many entries to launch when the single tokens are the decode kernel's, and when not."""
+    ``unit_slots`` = how many entries to launch when the single tokens are the decode kernel's, and when not.
+    ``softcap`` > 0: a score s becomes ``softcap * tanh(s / softcap)`` (after the scale).  ``slopes`` (float32
+    ``[num_heads]``): ``slopes[h] * (p - key)`` is taken off the scores of head h, a penalty linear in the distance.
+    ``gate`` (run dtype ``[T, num_heads]``): head h's output is multiplied by ``sigmoid(gate[t, h])``."""
     T = qkv.shape[0]
     S = ctx_lens.shape[0]
     _need(qkv, "qkv", None, (T, (num_heads + 2 * num_kv_heads) * head_dim))
@@ -443,7 +447,11 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
             _p(q_start), _p(ctx_lens), _p(seq_of_token), _p(positions), _i(T), _i(S),
             _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages), _f(scale),
             _i(0 if window is None else int(window)), _i(max_q_len), _i(max_ctx_len), _p(old_lens), _i(int(singles)),
-            _p(units), _i(int(unit_slots[0])), _i(int(unit_slots[1])), _stream(out))
+            _p(units), _i(int(unit_slots[0])), _i(int(unit_slots[1])), _f(float(softcap or 0.0)), _p(slopes), _p(gate), _stream(out))
+    if slopes is not None:
+        _need(slopes, "distance slopes", torch.float32, (num_heads,))
+    if gate is not None:
+        _need(gate, "head gate", qkv.dtype, (T, num_heads))
     if implementation is None:
         _check(library().li_paged_attention(*args), "paged_attention")
     else:
@@ -457,6 +465,180 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     _need(gate_up, "gate_up")
     _need(out, "swiglu output", gate_up.dtype, (T, I2 // 2))
     _check(library().li_swiglu(_p(gate_up), _p(out), _i(_dt(out)), _i(T), _i(I2 // 2), _stream(out)), "swiglu")
+
+
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
+    """out = g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit);
+    gate_up = [gate | up] along the last axis."""
+    T, I2 = gate_up.shape
+    _need(gate_up, "gate_up")
+    _need(out, "glu output", gate_up.dtype, (T, I2 // 2))
+    _check(library().li_glu_clamped(_p(gate_up), _p(out), _i(_dt(out)), _i(T), _i(I2 // 2), _f(limit), _f(alpha), _stream(out)), "glu_clamped")
+
+
+def weighted_sum2(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float, out: torch.Tensor) -> None:
+    """out = sa * a + sb * b (run dtype in and out, the sum in float32)."""
+    _need(a, "first operand")
+    _need(b, "second operand", a.dtype, a.shape)
+    _need(out, "weighted sum", a.dtype, a.shape)
+    _check(library().li_weighted_sum2(_p(a), _p(b), _f(sa), _f(sb), _p(out), _i(_dt(a)), _l(a.numel()), _stream(out)), "weighted_sum2")
+
+
+# --------------------------------------------------------------------------
+# several residual streams (hyper-connections) and learned positions
+# --------------------------------------------------------------------------
+
+def add_position_rows(x32: torch.Tensor, table: torch.Tensor, positions: torch.Tensor) -> None:
+    """x32[t] += table[positions[t]] (learned absolute positions; the table in the run dtype)."""
+    T, H = x32.shape
+    _need(x32, "residual stream", torch.float32)
+    _need(table, "position table", None, (table.shape[0], H))
+    _need(positions, "positions", torch.int32, (T,))
+    _check(library().li_add_position_rows(_p(x32), _p(table), _i(_dt(table)), _p(positions), _i(T), _i(H), _i(table.shape[0]), _stream(x32)),
+           "add_position_rows")
+
+
+def hc_expand(x32: torch.Tensor, xs: torch.Tensor) -> None:
+    """xs[t, a] = x32[t] for every stream a; xs float32 ``[T, streams, H]``."""
+    T, H = x32.shape
+    _need(x32, "residual stream", torch.float32)
+    _need(xs, "streams", torch.float32, (T, xs.shape[1], H))
+    _check(library().li_hc_expand(_p(x32), _p(xs), _i(T), _i(xs.shape[1]), _i(H), _stream(xs)), "hc_expand")
+
+
+def hc_read_norm(xs: torch.Tensor, in_w: Optional[torch.Tensor], rows: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                 out: torch.Tensor) -> None:
+    """out[r] = rmsnorm(sum_s in_w[s] xs[rows[r], s]) * weight.  ``in_w`` None: the plain sum of the streams;
+    ``rows`` None: every token in order."""
+    T, s, H = xs.shape
+    _need(xs, "streams", torch.float32)
+    if in_w is not None:
+        _need(in_w, "read weights", torch.float32, (s,))
+    R = T if rows is None else rows.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    _need(weight, "rmsnorm weight", torch.float32, (H,))
+    _need(out, "normalised output", None, (R, H))
+    _check(library().li_hc_read_norm(_p(xs), _p(in_w), _p(rows), _p(weight), _f(eps), _p(out), _i(_dt(out)), _i(R), _i(T), _i(s), _i(H),
+                                     _stream(out)), "hc_read_norm")
+
+
+def hc_update(xs: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_w: torch.Tensor, next_in: Optional[torch.Tensor] = None,
+              next_weight: Optional[torch.Tensor] = None, eps: float = 0.0, next_out: Optional[torch.Tensor] = None) -> None:
+    """xs[t, r] = sum_s mix[s, r] xs[t, s] + out_w[r] y[t], every stream from the old ones, in place; with ``next_out``
+    also the next sublayer's input: next_out[t] = rmsnorm(sum_r next_in[r] xs[t, r]) * next_weight."""
+    T, s, H = xs.shape
+    _need(xs, "streams", torch.float32)
+    _need(y, "sublayer output", None, (T, H))
+    _need(mix, "stream mix", torch.float32, (s, s))
+    _need(out_w, "write weights", torch.float32, (s,))
+    if next_out is not None:
+        _need(next_in, "read weights", torch.float32, (s,))
+        _need(next_weight, "rmsnorm weight", torch.float32, (H,))
+        _need(next_out, "normalised output", y.dtype, (T, H))
+    _check(library().li_hc_update(_p(xs), _p(y), _i(_dt(y)), _p(mix), _p(out_w), _p(next_in if next_out is not None else None),
+                                  _p(next_weight if next_out is not None else None), _f(eps), _p(next_out), _i(T), _i(s), _i(H), _stream(xs)),
+           "hc_update")
+
+
+# --------------------------------------------------------------------------
+# mixers with a state of fixed size per request
+# --------------------------------------------------------------------------
+
+def _state_args(state: torch.Tensor, offset: int):
+    _need(state, "state", torch.float32)
+    if state.dim() != 2:
+        raise KernelError(f"state must be [slots, elements], got {tuple(state.shape)}")
+    return _p(state), _l(state.shape[1]), _l(int(offset))
+
+
+def causal_conv_silu(x: torch.Tensor, col: int, weight: torch.Tensor, bias: torch.Tensor, state: torch.Tensor, state_off: int,
+                     q_start: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor, out: torch.Tensor) -> None:
+    """Depthwise causal convolution and silu over the C channels at column ``col`` of ``x`` [T, *]:
+    ``out[t, c] = silu(bias[c] + sum_k weight[c, k] * input_(t - taps + 1 + k)[c])``; inputs before a sequence's portion
+    come from ``state[slot, state_off:]`` ([taps - 1, C], oldest first).  The state is not changed
+    (:func:`conv_state_shift` does that afterwards)."""
+    T = x.shape[0]
+    C, taps = weight.shape
+    _need(x, "convolution input")
+    _need(weight, "convolution weight", torch.float32)
+    _need(bias, "convolution bias", torch.float32, (C,))
+    _need(out, "convolution output", x.dtype, (T, C))
+    _need(q_start, "q_start", torch.int32)
+    _need(seq_of_token, "seq_of_token", torch.int32, (T,))
+    _need(slots, "state slots", torch.int32)
+    st, stride, off = _state_args(state, state_off)
+    if state_off + (taps - 1) * C > state.shape[1]:
+        raise KernelError("causal_conv_silu: the state is too small for the convolution's inputs")
+    _check(library().li_causal_conv_silu(_p(x), _i(_dt(x)), _i(x.shape[1]), _i(col), _p(weight), _p(bias), st, stride, off, _p(q_start),
+                                         _p(seq_of_token), _p(slots), _p(out), _i(T), _i(C), _i(taps), _stream(out)), "causal_conv_silu")
+
+
+def conv_state_shift(x: torch.Tensor, col: int, channels: int, taps: int, state: torch.Tensor, state_off: int, q_start: torch.Tensor,
+                     slots: torch.Tensor) -> None:
+    """After a step's convolution: each sequence's state keeps the last ``taps - 1`` inputs it has now seen."""
+    _need(x, "convolution input")
+    _need(q_start, "q_start", torch.int32)
+    S = q_start.shape[0] - 1
+    _need(slots, "state slots", torch.int32, (S,))
+    st, stride, off = _state_args(state, state_off)
+    _check(library().li_conv_state_shift(_p(x), _i(_dt(x)), _i(x.shape[1]), _i(col), st, stride, off, _p(q_start), _p(slots), _i(S),
+                                         _i(channels), _i(taps), _stream(x)), "conv_state_shift")
+
+
+def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor,
+             state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, y32: torch.Tensor, heads: int, head_dim: int,
+             state_size: int, groups: int) -> None:
+    """The selective state-space recurrence per head, state ``S [state_size, head_dim]`` at the start of ``state[slot]``:
+    ``dt = softplus(proj[t, dt_col + h] + dt_bias[h])``; ``S = exp(-exp(A_log[h]) dt) S + dt B_t x_t^T``;
+    ``y_t = S^T C_t + D[h] x_t``.  ``xbc`` [T, heads * head_dim + 2 * groups * state_size] holds x | B | C."""
+    T, C = xbc.shape
+    _need(xbc, "x|B|C")
+    _need(proj, "projection", xbc.dtype)
+    for t, n in ((dt_bias, "dt_bias"), (A_log, "A_log"), (D, "D")):
+        _need(t, n, torch.float32, (heads,))
+    _need(y32, "scan output", torch.float32, (T, heads * head_dim))
+    S = q_start.shape[0] - 1
+    _need(slots, "state slots", torch.int32, (S,))
+    st, stride, _ = _state_args(state, 0)
+    if heads * head_dim * state_size > state.shape[1] or dt_col + heads > proj.shape[1]:
+        raise KernelError("ssm_scan: the state or the projection is too small")
+    dt_ptr = ctypes.c_void_p(proj.data_ptr() + dt_col * proj.element_size())
+    _check(library().li_ssm_scan(_p(xbc), _i(_dt(xbc)), _i(C), dt_ptr, _i(proj.shape[1]), _p(dt_bias), _p(A_log), _p(D), st, stride,
+                                 _p(q_start), _p(slots), _p(y32), _i(S), _i(heads), _i(head_dim), _i(state_size), _i(groups), _stream(y32)),
+           "ssm_scan")
+
+
+def decay_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
+               slots: torch.Tensor, out32: torch.Tensor, heads: int, dim: int, vdim: int) -> None:
+    """Linear attention with a constant decay per head, state ``S [dim, vdim]`` per head at the start of
+    ``state[slot]``: ``S = decay[h] S + k_t v_t^T``; ``out_t = S^T q_t``; q, k, v are silu of the columns of ``qkv``
+    at ``q_col``, ``k_col``, ``v_col`` (heads side by side)."""
+    T = qkv.shape[0]
+    _need(qkv, "q|k|v")
+    _need(decay, "decay", torch.float32, (heads,))
+    _need(out32, "scan output", torch.float32, (T, heads * vdim))
+    S = q_start.shape[0] - 1
+    _need(slots, "state slots", torch.int32, (S,))
+    st, stride, _ = _state_args(state, 0)
+    if heads * dim * vdim > state.shape[1]:
+        raise KernelError("decay_scan: the state is too small")
+    _check(library().li_decay_scan(_p(qkv), _i(_dt(qkv)), _i(qkv.shape[1]), _i(q_col), _i(k_col), _i(v_col), _p(decay), st, stride, _p(q_start),
+                                   _p(slots), _p(out32), _i(S), _i(heads), _i(dim), _i(vdim), _stream(out32)), "decay_scan")
+
+
+def gated_rmsnorm(y32: torch.Tensor, gate: torch.Tensor, gate_col: int, weight: torch.Tensor, eps: float, groups: int, gate_first: bool,
+                  out: torch.Tensor) -> None:
+    """RMSNorm of ``y32`` [T, n] in ``groups`` equal parts, times ``weight``.  ``gate_first``: y is multiplied by
+    silu(gate) before the norm; otherwise the normalised result is multiplied by sigmoid(gate).  The gate is the n
+    columns of ``gate`` from ``gate_col``."""
+    T, n = y32.shape
+    _need(y32, "norm input", torch.float32)
+    _need(gate, "gate")
+    _need(weight, "rmsnorm weight", torch.float32, (n,))
+    _need(out, "norm output", gate.dtype, (T, n))
+    _check(library().li_gated_rmsnorm(_p(y32), _p(gate), _i(_dt(gate)), _i(gate.shape[1]), _i(gate_col), _p(weight), _f(eps),
+                                      _i(0 if gate_first else 1), _p(out), _i(T), _i(n), _i(groups), _stream(out)), "gated_rmsnorm")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
@@ -559,7 +741,8 @@ TRACE = _env_on("LLAISYS_TRACE")          # LitInfer's other switch (src/llaisys
 
 _TIMED = ("embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "linear_add_scaled", "apply_row_scale",
           "rope_kv_write", "linear_rope_kv", "rope_table", "paged_attention", "swiglu", "argmax", "sample", "gather_rows", "scale_inplace",
-          "logit_cap")
+          "logit_cap", "glu_clamped", "weighted_sum2", "add_position_rows", "hc_expand", "hc_read_norm", "hc_update", "causal_conv_silu", "conv_state_shift",
+          "ssm_scan", "decay_scan", "gated_rmsnorm")
 if profile.enabled:
     for _name in _TIMED:
         globals()[_name] = profile.wrap(_name, globals()[_name])

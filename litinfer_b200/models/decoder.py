@@ -57,6 +57,8 @@ class DecoderModel:
         self.lm_head: Optional[torch.Tensor] = None
         self.head_is_tied = False
         self._fused = None                                     # models/fused_decode.py, made at the first step
+        # for looking inside a step: called with (schedule entry, residual stream, carry) after every block
+        self.observer = None
 
     # ------------------------------------------------------------------
     def params(self) -> List[ParamSpec]:
@@ -130,18 +132,26 @@ class DecoderModel:
             K.scale_inplace(x32, float(s.embedding_scale))
         if self.position is not None:
             self.position.add_to_stream(x32, ctx)
+        if s.streams > 1:
+            # several residual streams, all equal to the embedding at the start; the blocks work on [tokens, streams, width]
+            xs = torch.empty((ctx.num_tokens, s.streams, s.hidden_size), dtype=torch.float32, device=self.device)
+            K.hc_expand(x32, xs)
+            x32 = xs
         carry = None
         last = len(s.schedule) - 1
         for i, e in enumerate(s.schedule):
             # a block is told the first norm of the block that runs next, so that it can apply it in its own tail
             next_entry = self.blocks[s.schedule[i + 1].block].entry() if i < last else None
             x32, carry = self.blocks[e.block].forward(x32, ctx, caches[i], carry, next_entry)
+            if self.observer is not None:
+                self.observer(i, x32, carry)
         if carry is not None and carry.delta is not None:
             K.residual_add(x32, carry.delta)
         R = ctx.num_logit_rows
         logits = torch.empty((R, s.vocab_size), dtype=torch.float32, device=self.device)
         if R:
-            y = self.final_norm.gather_forward(x32, ctx.logit_rows)
+            # (several streams: the norm is of their sum)
+            y = self.final_norm.streams_forward(x32, None, ctx.logit_rows) if x32.dim() == 3 else self.final_norm.gather_forward(x32, ctx.logit_rows)
             K.linear(y, self.lm_head, None, logits)
             if s.logit_cap is not None:
                 K.logit_cap(logits, float(s.logit_cap))

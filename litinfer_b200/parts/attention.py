@@ -11,6 +11,17 @@ parameters of the spec; the position encoding is a part of its own, named by the
 (``position``; None: none) and asked only through :meth:`~litinfer_b200.parts.base.Position.rotary`.
 ``qkv_bias`` may be ``None``: the biases then follow the file, each on its own
 (LitInfer's linear takes a missing bias as none, src/llaisys/ops.cc:27-29).
+
+Further options of the spec, all off by default:
+
+* ``softcap``: a score s becomes ``softcap * tanh(s / softcap)`` after the scale;
+* ``distance_slopes`` (one number per head): ``slope_h * (i - j)`` is taken off the score of query i and key j;
+* ``head_gate`` (a tensor's stem): a map from the mixer's input to one number per head; head h's output is
+  multiplied by the sigmoid of its number before the output map;
+* ``value_dim``: values (and the heads of the output) of another size than queries and keys.  The cache, and the
+  kernels, have one head size: queries, keys and values are padded with zero rows of their matrices up to the larger
+  of the two (rounded up to a multiple of 16), and the output map gets zero columns there, which changes no sum;
+* ``suffixes``: what follows a stem in the names of weights and biases.
 """
 
 from __future__ import annotations
@@ -35,23 +46,36 @@ class PagedAttention(Mixer):
         self.num_heads = int(spec["num_heads"])
         self.ctas_per_work_unit = self.num_heads           # the kernel for long portions runs one CTA per head and entry
         self.num_kv_heads = int(spec["num_kv_heads"])
-        self.head_dim = int(spec["head_dim"])
+        self.qk_dim = int(spec["head_dim"])
+        self.value_dim = int(spec.get("value_dim") or self.qk_dim)
+        # one head size for the cache and the kernels: see the module's text
+        self.head_dim = self.qk_dim if self.value_dim == self.qk_dim else -(-max(self.qk_dim, self.value_dim) // 16) * 16
         self.scale = float(spec["scale"])
+        self.softcap = float(spec.get("softcap") or 0.0)
+        slopes = spec.get("distance_slopes")
+        if slopes is not None and len(slopes) != self.num_heads:
+            raise ValueError(f"{len(slopes)} distance slopes for {self.num_heads} heads")
+        self.slopes = torch.tensor([float(x) for x in slopes], dtype=torch.float32, device=self.device) if slopes is not None else None
         self.window = spec.get("window")
         if self.num_heads % self.num_kv_heads:
             raise ValueError(f"{self.num_heads} heads are not a multiple of {self.num_kv_heads} key/value heads")
         names = spec.get("names", {})
+        suffixes = tuple(spec.get("suffixes", (".weight", ".bias")))
         self.q_dim = self.num_heads * self.head_dim
         self.kv_dim = self.num_kv_heads * self.head_dim
         self.qkv = FusedLinear(
             prefix, [names.get("q", "q_proj"), names.get("k", "k_proj"), names.get("v", "v_proj")],
-            self.hidden, [self.q_dim, self.kv_dim, self.kv_dim], spec.get("qkv_bias", False), dtype)
-        self.out = FusedLinear(prefix, [names.get("o", "o_proj")], self.q_dim, [self.hidden], bool(spec.get("out_bias", False)), dtype)
+            self.hidden, [self.num_heads * self.qk_dim, self.num_kv_heads * self.qk_dim, self.num_kv_heads * self.value_dim],
+            spec.get("qkv_bias", False), dtype, suffixes=suffixes)
+        self.out = FusedLinear(prefix, [names.get("o", "o_proj")], self.num_heads * self.value_dim, [self.hidden],
+                               bool(spec.get("out_bias", False)), dtype, suffixes=suffixes)
+        gate = spec.get("head_gate")
+        self.gate = FusedLinear(prefix, [gate], self.hidden, [self.num_heads], False, dtype, suffixes=suffixes) if gate else None
         position = spec.get("position")
         self.position = POSITIONS.build(position, prefix, dtype, device, head_dim=self.head_dim) if position is not None else None
 
     def params(self) -> List[ParamSpec]:
-        return self.qkv.params() + self.out.params()
+        return self.qkv.params() + self.out.params() + (self.gate.params() if self.gate is not None else [])
 
     def parts(self):
         return [self.position] if self.position is not None else []
@@ -59,6 +83,35 @@ class PagedAttention(Mixer):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.qkv.bind(tensors)
         self.out.bind(tensors)
+        if self.gate is not None:
+            self.gate.bind(tensors)
+        if self.head_dim != self.qk_dim or self.head_dim != self.value_dim:
+            self._pad_heads()
+
+    def _pad_heads(self) -> None:
+        """Zero rows (q, k, v, with their biases) and zero columns (output map) up to the one head size of the cache."""
+        D, nh, nkv = self.head_dim, self.num_heads, self.num_kv_heads
+
+        def rows(t, heads, d):
+            if t is None:
+                return None
+            out = torch.zeros((heads, D) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+            out[:, :d] = t.view(heads, d, *t.shape[1:])
+            return out.view(heads * D, *t.shape[1:])
+
+        cuts = (nh * self.qk_dim, nkv * self.qk_dim, nkv * self.value_dim)
+        shapes = ((nh, self.qk_dim), (nkv, self.qk_dim), (nkv, self.value_dim))
+        w = torch.split(self.qkv.weight, cuts, dim=0)
+        self.qkv.weight = torch.cat([rows(t, *sh) for t, sh in zip(w, shapes)], dim=0).contiguous()
+        if self.qkv.bias is not None:
+            b = torch.split(self.qkv.bias, cuts, dim=0)
+            self.qkv.bias = torch.cat([rows(t, *sh) for t, sh in zip(b, shapes)], dim=0).contiguous()
+        self.qkv.out_features = self.qkv.weight.shape[0]
+        o = self.out.weight.view(self.hidden, nh, self.value_dim)
+        padded = torch.zeros((self.hidden, nh, D), dtype=o.dtype, device=o.device)
+        padded[:, :, :self.value_dim] = o
+        self.out.weight = padded.view(self.hidden, nh * D).contiguous()
+        self.out.in_features = nh * D
 
     def cache_requirement(self):
         return PagedKV(self.num_kv_heads, self.head_dim, self.window)
@@ -66,6 +119,8 @@ class PagedAttention(Mixer):
     def fused_decode(self):
         rope = self.position.fused_decode() if self.position is not None else None
         if type(self) is not PagedAttention or rope is None or rope["rotary_dim"] != self.head_dim or self.out.bias is not None:
+            return None
+        if self.softcap or self.slopes is not None or self.gate is not None or self.value_dim != self.qk_dim:
             return None
         return {"w_qkv": self.qkv.weight, "b_qkv": self.qkv.bias, "w_o": self.out.weight, "hidden": self.hidden, "heads": self.num_heads,
                 "kv_heads": self.num_kv_heads, "head_dim": self.head_dim, "scale": self.scale, "window": self.window,
@@ -80,6 +135,7 @@ class PagedAttention(Mixer):
     def _attend(self, h, ctx, cache):
         """Everything before the output projection: [tokens, heads * head_dim]."""
         view = ctx.group(cache.group)
+        gate = self.gate(h) if self.gate is not None else None        # (a deferred activation: the product applies its factor)
         h, row_scale = undefer(h, self.qkv.weight)
         qkv = torch.empty((h.shape[0], self.qkv.out_features), dtype=self.dtype, device=h.device)
         # projection, position encoding of q and k, k and v into the cache: one call (and for few tokens one kernel)
@@ -93,5 +149,5 @@ class PagedAttention(Mixer):
             qkv, o, cache.k, cache.v, view.block_table, ctx.q_start, ctx.ctx_lens, ctx.seq_of_token, ctx.positions,
             self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window,
             ctx.max_q_len, ctx.max_ctx_len, old_lens=ctx.old_lens, singles=ctx.num_single,
-            units=ctx.attn_units, unit_slots=ctx.attn_unit_slots)
+            units=ctx.attn_units, unit_slots=ctx.attn_unit_slots, softcap=self.softcap, slopes=self.slopes, gate=gate)
         return o

@@ -71,6 +71,20 @@ class FixedState:
     dtype: torch.dtype = torch.float32
 
 
+def requirement_parts(req) -> tuple:
+    """A cache requirement as a tuple of single ones: a mixer made of several mixers asks for a tuple (keys and values
+    in pages for one of them, a state of fixed size for another), a plain one for a single requirement or None."""
+    if req is None:
+        return ()
+    if isinstance(req, (tuple, list)):
+        return tuple(r for part in req for r in requirement_parts(part))
+    return (req,)
+
+
+def has_fixed_state(req) -> bool:
+    return any(isinstance(r, FixedState) for r in requirement_parts(req))
+
+
 # --------------------------------------------------------------------------
 # base class
 # --------------------------------------------------------------------------
@@ -179,7 +193,8 @@ class Mixer(Part):
     decodes_from_device = False
 
     def cache_requirement(self):
-        """PagedKV, FixedState or None."""
+        """PagedKV, FixedState, None, or a tuple of these (one per mixer inside this one: the cache it is handed then
+        has ``parts``, in the same order)."""
         return None
 
     def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:
@@ -213,6 +228,16 @@ class Norm(Part):
         """``x32 += linear(a)``; the norm of the sum, which may be :class:`Deferred` if ``defer``.
         ``linear`` is a :class:`~litinfer_b200.parts.linear.FusedLinear`."""
         return self.add_forward(x32, linear(a))
+
+    # A residual stream kept as several streams xs [tokens, streams, width] (hyper-connections): the norm of a weighted
+    # sum of the streams (``read`` None: their plain sum; ``rows``: of these tokens only), and the same after a
+    # sublayer's output y has been written back (xs[r] = sum_s mix[s, r] xs[s] + write[r] y, in place).
+    def streams_forward(self, xs: torch.Tensor, read: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+    def streams_update_forward(self, xs: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, write: torch.Tensor,
+                               read: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
 
 
 @dataclass

@@ -17,6 +17,13 @@ from __future__ import annotations
 
 from typing import List
 
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import torch
+
+from .. import kernels as K
+from ..weights.loader import ParamSpec
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Carry, Tail
 
 
@@ -59,3 +66,97 @@ class PreNormBlock(Block):
         if next_entry is None:
             return x32, Carry(delta=self.feed_forward.forward(h, ctx))
         return x32, Carry(normed=self.feed_forward.forward_into(h, ctx, Tail(x32, next_entry.norm, next_entry.defer)))
+
+
+@dataclass
+class StreamsEntry(Tail):
+    """The entry of a block that keeps several residual streams: its first norm and the weights with which its first
+    sublayer reads the streams, so that the block before can do that read in the pass that writes its own output back."""
+
+    read: Optional[torch.Tensor] = None
+
+
+class _Connection:
+    """The tensors that tie one sublayer to the streams: read weights [s], write weights [s], mix [s, s] (from, to)."""
+
+    def __init__(self, prefix: str, streams: int, names: Dict[str, str]) -> None:
+        self.streams = streams
+        self.names = {k: prefix + names.get(k, k) for k in ("in", "out", "mix")}
+        self.read = self.write = self.mix = None
+
+    def params(self):
+        s = self.streams
+        return [ParamSpec(self.names["in"], (s,), role="vector", mean=1.0 / s, std=0.05),
+                ParamSpec(self.names["out"], (s,), role="vector", init="ones_normal"),
+                ParamSpec(self.names["mix"], (s, s), role="vector", init="eye_normal", std=0.05)]
+
+    def bind(self, tensors) -> None:
+        self.read, self.write, self.mix = (tensors.pop(self.names[k]) for k in ("in", "out", "mix"))
+
+
+@BLOCKS.register("hyper_prenorm")
+class HyperPreNormBlock(Block):
+    """Pre-norm sublayers over several residual streams (hyper-connections).  Instead of one stream x there are s
+    copies, ``xs [tokens, s, width]``, all equal to the embedding at the start and summed at the end.  A sublayer
+    (the mixer, then the feed-forward if the layer has one) reads ``u = sum_s in[s] xs[s]``, runs on ``norm(u)``, and its
+    output y goes back as ``xs'[r] = sum_s mix[s, r] xs[s] + out[r] y``, every stream from the old ones.  Each sublayer has
+    its own in / out / mix tensors (roles ``mixer_connection`` and ``feed_forward_connection`` give their prefixes).
+
+    The write-back of a sublayer and the read and norm of the next one are one kernel (as add + norm is for a single
+    stream); told the next block's entry, the last sublayer of this block does the next block's first read."""
+
+    def __init__(self, spec, prefix, dtype, device):
+        super().__init__(spec, prefix, dtype, device)
+        self.mixer_norm = self.build(NORMS, "mixer_norm")
+        self.mixer = self.build(MIXERS, "mixer")
+        self.feed_forward = self.build(FEED_FORWARDS, "feed_forward", required=False)
+        self.feed_forward_norm = self.build(NORMS, "feed_forward_norm", required=self.feed_forward is not None)
+        conn = spec.part("connections")
+        if conn is None:
+            raise ValueError(f"block 'hyper_prenorm' at {spec.prefix!r} needs a part 'connections' with the number of streams")
+        self.streams = int(conn["streams"])
+        names = conn.get("names", {})
+        self.mixer_connection = _Connection(spec.prefix_of("mixer_connection"), self.streams, names)
+        self.feed_forward_connection = (_Connection(spec.prefix_of("feed_forward_connection"), self.streams, names)
+                                        if self.feed_forward is not None else None)
+
+    def parts(self) -> List:
+        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None]
+
+    def params(self):
+        out = self.mixer_connection.params()
+        if self.feed_forward_connection is not None:
+            out += self.feed_forward_connection.params()
+        return out
+
+    def bind(self, tensors) -> None:
+        self.mixer_connection.bind(tensors)
+        if self.feed_forward_connection is not None:
+            self.feed_forward_connection.bind(tensors)
+
+    def entry(self):
+        return StreamsEntry(None, self.mixer_norm, False, read=self.mixer_connection.read)
+
+    @staticmethod
+    def _write_back(xs, y, conn, next_norm, next_read):
+        """The sublayer's output into the streams; the next sublayer's input if its norm and read weights are known."""
+        if next_norm is None:
+            K.hc_update(xs, y, conn.mix, conn.write)
+            return None
+        return next_norm.streams_update_forward(xs, y, conn.mix, conn.write, next_read)
+
+    def forward(self, xs, ctx, cache, carry, next_entry=None):
+        if xs.dim() != 3 or xs.shape[1] != self.streams:
+            raise ValueError(f"a block over {self.streams} streams was handed a residual of shape {tuple(xs.shape)}")
+        if carry is not None and carry.delta is not None:
+            raise ValueError("a block over several streams cannot take an output that is still to be added")
+        h = carry.normed if carry is not None and carry.normed is not None else self.mixer_norm.streams_forward(xs, self.mixer_connection.read)
+        nxt = next_entry if isinstance(next_entry, StreamsEntry) else None
+        y = self.mixer.forward(h, ctx, cache)
+        if self.feed_forward is None:
+            h = self._write_back(xs, y, self.mixer_connection, nxt.norm if nxt else None, nxt.read if nxt else None)
+            return xs, (Carry(normed=h) if h is not None else None)
+        h = self._write_back(xs, y, self.mixer_connection, self.feed_forward_norm, self.feed_forward_connection.read)
+        y = self.feed_forward.forward(h, ctx)
+        h = self._write_back(xs, y, self.feed_forward_connection, nxt.norm if nxt else None, nxt.read if nxt else None)
+        return xs, (Carry(normed=h) if h is not None else None)

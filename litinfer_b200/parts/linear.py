@@ -28,10 +28,12 @@ def undefer(x, weight: torch.Tensor):
 class FusedLinear:
     """``names``: tensor-name stems (without .weight / .bias); ``outs``: their output sizes.
     ``bias``: True (each map has one), False (none), or None: the biases follow the file, each map on
-    its own; a map without one counts as zeros when another has one."""
+    its own; a map without one counts as zeros when another has one.  ``suffixes``: what follows a stem in the
+    names of its weight and its bias."""
 
     def __init__(self, prefix: str, names: Sequence[str], in_features: int, outs: Sequence[int], bias: Optional[bool],
-                 dtype: torch.dtype, std: float = 0.02) -> None:
+                 dtype: torch.dtype, std: float = 0.02, suffixes: Tuple[str, str] = (".weight", ".bias")) -> None:
+        self.w_suffix, self.b_suffix = suffixes
         self.prefix = prefix
         self.names = list(names)
         self.in_features = int(in_features)
@@ -47,17 +49,17 @@ class FusedLinear:
     def params(self) -> List[ParamSpec]:
         out = []
         for n, o in zip(self.names, self.outs):
-            out.append(ParamSpec(f"{self.prefix}{n}.weight", (o, self.in_features), role="matrix", std=self.std))
+            out.append(ParamSpec(f"{self.prefix}{n}{self.w_suffix}", (o, self.in_features), role="matrix", std=self.std))
             if self.has_bias:
-                out.append(ParamSpec(f"{self.prefix}{n}.bias", (o,), role="vector", std=self.std, optional=self.bias_optional))
+                out.append(ParamSpec(f"{self.prefix}{n}{self.b_suffix}", (o,), role="vector", std=self.std, optional=self.bias_optional))
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        ws = [tensors.pop(f"{self.prefix}{n}.weight") for n in self.names]
+        ws = [tensors.pop(f"{self.prefix}{n}{self.w_suffix}") for n in self.names]
         self.weight = ws[0] if len(ws) == 1 else torch.cat(ws, dim=0).contiguous()
         del ws
         if self.has_bias:
-            bs = [tensors.pop(f"{self.prefix}{n}.bias", None) if self.bias_optional else tensors.pop(f"{self.prefix}{n}.bias")
+            bs = [tensors.pop(f"{self.prefix}{n}{self.b_suffix}", None) if self.bias_optional else tensors.pop(f"{self.prefix}{n}{self.b_suffix}")
                   for n in self.names]
             if all(b is None for b in bs):
                 self.bias = None
@@ -80,16 +82,16 @@ class GateUpLinear(FusedLinear):
     epilogue applies up * silu(gate), so the [tokens, 2 * intermediate] product never goes to
     memory.  Otherwise (the 32-bit path) the fused product is followed by the swiglu kernel."""
 
-    def __init__(self, prefix, gate_name, up_name, in_features, intermediate, dtype, std=0.02):
-        super().__init__(prefix, [gate_name, up_name], in_features, [intermediate, intermediate], False, dtype, std)
+    def __init__(self, prefix, gate_name, up_name, in_features, intermediate, dtype, std=0.02, suffixes=(".weight", ".bias")):
+        super().__init__(prefix, [gate_name, up_name], in_features, [intermediate, intermediate], False, dtype, std, suffixes)
         self.intermediate = int(intermediate)
         self.fused_activation = dtype == torch.bfloat16 and intermediate % 8 == 0 and in_features % 8 == 0
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         if not self.fused_activation:
             return super().bind(tensors)
-        gate = tensors.pop(f"{self.prefix}{self.names[0]}.weight")
-        up = tensors.pop(f"{self.prefix}{self.names[1]}.weight")
+        gate = tensors.pop(f"{self.prefix}{self.names[0]}{self.w_suffix}")
+        up = tensors.pop(f"{self.prefix}{self.names[1]}{self.w_suffix}")
         self.weight = K.interleave_gate_up(gate, up)
 
     def activation(self, x: torch.Tensor) -> torch.Tensor:

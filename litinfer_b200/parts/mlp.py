@@ -45,3 +45,35 @@ class SwiGLU(FeedForward):
 
     def forward_into(self, h, ctx, tail):
         return tail.apply_linear(self.down, self.gate_up.activation(h))
+
+
+@FEED_FORWARDS.register("clamped_glu")
+class ClampedGLU(FeedForward):
+    """A gated feed-forward with bounded operands: g = min(gate(h), limit), u = clamp(up(h), -limit, limit),
+    y = g * sigmoid(alpha * g) * (u + 1), output down(y); no biases.  ``limit`` and ``alpha`` are parameters of the spec.
+    gate and up are one product; the activation is computed in float32 and rounded once."""
+
+    def __init__(self, spec, prefix, dtype, device):
+        super().__init__(spec, prefix, dtype, device)
+        self.hidden = int(spec["hidden_size"])
+        self.intermediate = int(spec["intermediate_size"])
+        self.limit = float(spec["limit"])
+        self.alpha = float(spec.get("alpha", 1.702))
+        names = spec.get("names", {})
+        suffixes = tuple(spec.get("suffixes", (".weight", ".bias")))
+        self.gate_up = FusedLinear(prefix, [names.get("gate", "gate_proj"), names.get("up", "up_proj")], self.hidden,
+                                   [self.intermediate, self.intermediate], False, dtype, suffixes=suffixes)
+        self.down = FusedLinear(prefix, [names.get("down", "down_proj")], self.intermediate, [self.hidden], False, dtype, suffixes=suffixes)
+
+    def params(self) -> List[ParamSpec]:
+        return self.gate_up.params() + self.down.params()
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.gate_up.bind(tensors)
+        self.down.bind(tensors)
+
+    def forward(self, h, ctx):
+        both = self.gate_up(h)
+        act = torch.empty((both.shape[0], self.intermediate), dtype=self.dtype, device=both.device)
+        K.glu_clamped(both, act, self.limit, self.alpha)
+        return self.down(act)

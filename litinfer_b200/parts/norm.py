@@ -31,13 +31,14 @@ class RMSNorm(Norm):
         super().__init__(spec, prefix, dtype, device)
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
+        self.tensor = self.prefix + str(spec.get("tensor", "weight"))      # the weight's name below the prefix
         self.weight = None
 
     def params(self) -> List[ParamSpec]:
-        return [ParamSpec(self.prefix + "weight", (self.size,), role="vector", init="ones_normal")]
+        return [ParamSpec(self.tensor, (self.size,), role="vector", init="ones_normal")]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors.pop(self.prefix + "weight")
+        self.weight = tensors.pop(self.tensor)
 
     def fused_decode(self):
         return {"weight": self.weight, "eps": self.eps, "size": self.size} if type(self) is RMSNorm and self.weight is not None else None
@@ -63,6 +64,16 @@ class RMSNorm(Norm):
                 K.linear_add_scaled(a, linear.weight, linear.bias, x32, self.weight, h, ssq)
                 return Deferred(h, ssq, self.size, self.eps)
         return self.add_forward(x32, linear(a))
+
+    def streams_forward(self, xs, read, rows=None):
+        out = torch.empty((xs.shape[0] if rows is None else rows.shape[0], xs.shape[2]), dtype=self.dtype, device=xs.device)
+        K.hc_read_norm(xs, read, rows, self.weight, self.eps, out)
+        return out
+
+    def streams_update_forward(self, xs, y, mix, write, read):
+        out = torch.empty((xs.shape[0], xs.shape[2]), dtype=self.dtype, device=xs.device)
+        K.hc_update(xs, y, mix, write, read, self.weight, self.eps, out)
+        return out
 
     def gather_forward(self, x32, rows):
         out = torch.empty((rows.shape[0], x32.shape[1]), dtype=self.dtype, device=x32.device)

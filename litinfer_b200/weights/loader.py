@@ -60,8 +60,9 @@ class ParamSpec:
     name: str
     shape: Tuple[int, ...]
     role: str = "matrix"            # matrix | vector | table | keep
-    init: str = "normal"            # normal | ones_normal | zeros | randint
+    init: str = "normal"            # normal | ones_normal | eye_normal (a square matrix: identity + normal) | zeros | randint
     std: float = 0.02
+    mean: float = 0.0               # of init "normal"
     optional: bool = False          # the file may lack it (the part then does without)
     aliases: Tuple[str, ...] = ()   # other names it may be stored under, tried in order after ``name``
     draw: bool = True               # whether random-weights mode makes one (an optional tensor may say no)

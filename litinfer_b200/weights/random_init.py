@@ -162,8 +162,15 @@ def random_tensor(p: ParamSpec, seed: int, device="cpu", dtype: torch.dtype = to
             K.fill_randint(out, key, RANDINT_RANGE)
             return out
         return _host_randint(key, n).reshape(p.shape).to(dev)
+    if p.init == "eye_normal":
+        if len(p.shape) != 2 or p.shape[0] != p.shape[1]:
+            raise ValueError(f"init eye_normal of tensor {p.name} needs a square matrix, got {tuple(p.shape)}")
+        from dataclasses import replace
+
+        noise = random_tensor(replace(p, init="normal", mean=0.0), seed, device, torch.float32)
+        return (noise + torch.eye(p.shape[0], dtype=torch.float32, device=dev)).to(dtype)
     if p.init == "normal":
-        mean, std = 0.0, float(p.std)
+        mean, std = float(p.mean), float(p.std)
     elif p.init == "ones_normal":
         mean, std = 1.0, 0.1
     else:

@@ -140,7 +140,7 @@ def rope_table(positions, denominators, out):
 
 def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
                     num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len, implementation=None, old_lens=None, singles=0,
-                    units=None, unit_slots=(0, 0)):
+                    units=None, unit_slots=(0, 0), softcap=0.0, slopes=None, gate=None):
     # old_lens only tells a kernel which keys it may read early, singles which kernel takes which sequence, units how a
     # kernel shares its work out; the result does not depend on them
     T = qkv.shape[0]
@@ -160,14 +160,20 @@ def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, 
         v = v_cache[pages, :, :, offs].float()
         for h in range(num_heads):
             sc = (k[:, h // group] @ q[t, h]) * scale
+            if softcap:
+                sc = softcap * torch.tanh(sc / softcap)
+            if slopes is not None:
+                sc = sc - slopes[h] * (p - keys).float()
             pr = torch.softmax(sc, dim=0)
             res[t, h] = pr @ v[:, h // group]
+            if gate is not None:
+                res[t, h] *= torch.sigmoid(gate[t, h].float())
     _store(out, res.reshape(T, num_heads * head_dim))
 
 
 def paged_attention_dense(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
                           num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len, implementation=None, old_lens=None,
-                          singles=0, units=None, unit_slots=(0, 0)):
+                          singles=0, units=None, unit_slots=(0, 0), softcap=0.0, slopes=None, gate=None):
     """The same formula as :func:`paged_attention`, a sequence at a time instead of a token and a head at a time (for
     contexts of thousands of keys): scores of all the sequence's tokens against all its keys in float32, keys outside
     [p - window + 1, p] masked, softmax, weighted sum."""
@@ -188,11 +194,17 @@ def paged_attention_dense(qkv, out, k_cache, v_cache, block_table, q_start, ctx_
         v = v_cache[pages, :, :, offs].float().repeat_interleave(group, dim=1)
         pos = positions[lo:hi].long()
         sc = torch.einsum("thd,chd->htc", q[lo:hi], k) * scale
+        if softcap:
+            sc = softcap * torch.tanh(sc / softcap)
+        if slopes is not None:
+            sc = sc - slopes[:, None, None] * (pos[:, None] - keys[None, :]).float()[None]
         seen = keys[None, :] <= pos[:, None]
         if window:
             seen &= keys[None, :] > pos[:, None] - window
         sc = sc.masked_fill(~seen[None], float("-inf"))
         res[lo:hi] = torch.einsum("htc,chd->thd", torch.softmax(sc, dim=-1), v)
+        if gate is not None:
+            res[lo:hi] *= torch.sigmoid(gate[lo:hi].float())[:, :, None]
     _store(out, res.reshape(T, num_heads * head_dim))
 
 
@@ -212,6 +224,113 @@ def swiglu(gate_up, out):
     I = gate_up.shape[1] // 2
     g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
     _store(out, u * (g / (1.0 + torch.exp(-g))))
+
+
+def glu_clamped(gate_up, out, limit, alpha):
+    I = gate_up.shape[1] // 2
+    g = torch.clamp(gate_up[:, :I].float(), max=limit)
+    u = torch.clamp(gate_up[:, I:].float(), min=-limit, max=limit)
+    _store(out, g * torch.sigmoid(alpha * g) * (u + 1.0))
+
+
+def weighted_sum2(a, b, sa, sb, out):
+    _store(out, sa * a.float() + sb * b.float())
+
+
+def add_position_rows(x32, table, positions):
+    x32.add_(table[positions.long()].float())
+
+
+def hc_expand(x32, xs):
+    xs.copy_(x32[:, None, :].expand_as(xs))
+
+
+def hc_read_norm(xs, in_w, rows, weight, eps, out):
+    src = xs if rows is None else xs[rows.long()]
+    u = src.sum(dim=1) if in_w is None else torch.einsum("s,tsw->tw", in_w, src)
+    _store(out, _rms(u, weight, eps))
+
+
+def hc_update(xs, y, mix, out_w, next_in=None, next_weight=None, eps=0.0, next_out=None):
+    new = torch.einsum("sr,tsw->trw", mix, xs) + out_w[None, :, None] * y.float()[:, None, :]
+    xs.copy_(new)
+    if next_out is not None:
+        _store(next_out, _rms(torch.einsum("s,tsw->tw", next_in, xs), next_weight, eps))
+
+
+def _silu(x):
+    return x * torch.sigmoid(x)
+
+
+def causal_conv_silu(x, col, weight, bias, state, state_off, q_start, seq_of_token, slots, out):
+    C, taps = weight.shape
+    starts, sl = q_start.tolist(), slots.tolist()
+    for s in range(len(starts) - 1):
+        lo, hi = starts[s], starts[s + 1]
+        if hi == lo:
+            continue
+        before = state[sl[s], state_off:state_off + (taps - 1) * C].view(taps - 1, C)
+        seq = torch.cat([before, x[lo:hi, col:col + C].float()], dim=0)
+        acc = bias[None, :].expand(hi - lo, C).clone()
+        for k in range(taps):
+            acc += weight[:, k][None, :] * seq[k:k + hi - lo]
+        _store(out[lo:hi], _silu(acc))
+
+
+def conv_state_shift(x, col, channels, taps, state, state_off, q_start, slots):
+    starts, sl = q_start.tolist(), slots.tolist()
+    for s in range(len(starts) - 1):
+        lo, hi = starts[s], starts[s + 1]
+        if hi == lo or taps == 1:
+            continue
+        view = state[sl[s], state_off:state_off + (taps - 1) * channels].view(taps - 1, channels)
+        seq = torch.cat([view, x[lo:hi, col:col + channels].float()], dim=0)
+        view.copy_(seq[-(taps - 1):])
+
+
+def ssm_scan(xbc, proj, dt_col, dt_bias, A_log, D, state, q_start, slots, y32, heads, head_dim, state_size, groups):
+    starts, sl = q_start.tolist(), slots.tolist()
+    inner, P, N = heads * head_dim, head_dim, state_size
+    rate = torch.exp(A_log)
+    per = heads // groups
+    for s in range(len(starts) - 1):
+        lo, hi = starts[s], starts[s + 1]
+        if hi == lo:
+            continue
+        S = state[sl[s], :heads * N * P].view(heads, N, P)
+        for t in range(lo, hi):
+            row = xbc[t].float()
+            x = row[:inner].view(heads, P)
+            B = row[inner:inner + groups * N].view(groups, N).repeat_interleave(per, dim=0)
+            Cm = row[inner + groups * N:].view(groups, N).repeat_interleave(per, dim=0)
+            dt = torch.nn.functional.softplus(proj[t, dt_col:dt_col + heads].float() + dt_bias, threshold=1e9)
+            S.mul_(torch.exp(-rate * dt)[:, None, None]).add_((dt[:, None] * B)[:, :, None] * x[:, None, :])
+            y32[t] = (torch.einsum("hnp,hn->hp", S, Cm) + D[:, None] * x).reshape(inner)
+
+
+def decay_scan(qkv, q_col, k_col, v_col, decay, state, q_start, slots, out32, heads, dim, vdim):
+    starts, sl = q_start.tolist(), slots.tolist()
+    for s in range(len(starts) - 1):
+        lo, hi = starts[s], starts[s + 1]
+        if hi == lo:
+            continue
+        S = state[sl[s], :heads * dim * vdim].view(heads, dim, vdim)
+        for t in range(lo, hi):
+            row = qkv[t].float()
+            q = _silu(row[q_col:q_col + heads * dim]).view(heads, dim)
+            k = _silu(row[k_col:k_col + heads * dim]).view(heads, dim)
+            v = _silu(row[v_col:v_col + heads * vdim]).view(heads, vdim)
+            S.mul_(decay[:, None, None]).add_(k[:, :, None] * v[:, None, :])
+            out32[t] = torch.einsum("hdv,hd->hv", S, q).reshape(heads * vdim)
+
+
+def gated_rmsnorm(y32, gate, gate_col, weight, eps, groups, gate_first, out):
+    T, n = y32.shape
+    z = gate[:, gate_col:gate_col + n].float()
+    v = y32 * _silu(z) if gate_first else y32
+    v = v.view(T, groups, n // groups)
+    v = (v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)).reshape(T, n) * weight
+    _store(out, v if gate_first else v * torch.sigmoid(z))
 
 
 def argmax(logits, out):
@@ -303,5 +422,6 @@ def table_gather(resident, updates, slots, out, trash_page):
             out[s, b] = resident[slot, b] if b < cols else trash_page
 
 
-ALL = ["table_gather", "gather_rows", "scale_inplace", "logit_cap", "rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
+ALL = ["glu_clamped", "weighted_sum2", "add_position_rows", "hc_expand", "hc_read_norm", "hc_update", "causal_conv_silu", "conv_state_shift", "ssm_scan",
+       "decay_scan", "gated_rmsnorm", "table_gather", "gather_rows", "scale_inplace", "logit_cap", "rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]
