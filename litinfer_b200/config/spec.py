@@ -126,8 +126,9 @@ class ModelSpec:
     embedding_scale: Optional[float] = None
     logit_cap: Optional[float] = None
     # the residual stream is kept as this many streams (hyper-connections): copies of the embedding at the start, their
-    # sum at the end; every block then is of an arrangement that takes them
-    streams: int = 1
+    # sum at the end; every block then is of an arrangement that takes them (also for 1, where those arrangements still
+    # weigh what they read and write).  None: the plain single stream
+    streams: Optional[int] = None
     # other names under which a declared tensor may be stored: declared name -> names tried after it
     aliases: Mapping[str, Tuple[str, ...]] = field(default_factory=dict)
 

@@ -132,7 +132,7 @@ class DecoderModel:
             K.scale_inplace(x32, float(s.embedding_scale))
         if self.position is not None:
             self.position.add_to_stream(x32, ctx)
-        if s.streams > 1:
+        if s.streams is not None:
             # several residual streams, all equal to the embedding at the start; the blocks work on [tokens, streams, width]
             xs = torch.empty((ctx.num_tokens, s.streams, s.hidden_size), dtype=torch.float32, device=self.device)
             K.hc_expand(x32, xs)
