@@ -25,6 +25,10 @@ Weights (3 GB) are larger than L2, so nothing stays cached between steps.
 profiling runs and the summaries under ``profiles/``); ``mixed`` is a step of ``--batch`` requests decoding at
 ``--context`` beside a portion of ``--prefill-tokens`` prompt tokens.
 
+``--only design`` runs the Filasun design beside the Qwen2 model of equal layer sizes and layer count (``--design-shapes``,
+``--layers``, default 6): prefill of ``--prefill-tokens`` tokens and decode at batch 1, 8 and 32; ``--arch filasun`` puts
+that design behind ``--only decode|prefill|kernels-decode|kernels-prefill`` (the kernel tables of ``profiles/``).
+
 ``--shape 1.5b|7b|14b`` chooses the layer sizes (default 1.5b, the headline; the other two are the larger workloads of
 the benchmark description and run behind the flag only):
 
@@ -84,6 +88,56 @@ SHAPES = {
     "14b": dict(name="Qwen2.5-14B shape", num_hidden_layers=48, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, head_dim=128,
                 intermediate_size=13824, vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-5, max_position_embeddings=8192),
 }
+
+
+def filasun_config(shape: str, layers: int, window: int = 1024):
+    """A Filasun model with the layer sizes of a shape of the benchmark description: the same width, heads, key/value
+    heads, head size, feed-forward width and vocabulary as the Qwen2 model of that shape; every third layer a
+    selective state-space layer (heads of 64, a state of 128, no feed-forward), the others a windowed-attention and a
+    decayed linear-attention mixer side by side with the gated feed-forward; four residual streams."""
+    d = SHAPES[shape]
+    H, nh, nkv, dh = d["hidden_size"], d["num_attention_heads"], d["num_key_value_heads"], d["head_dim"]
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": d["intermediate_size"], "limit": 7.0},
+           "mixer": {"left": {"heads": nh, "kv_heads": nkv, "dim": dh, "vdim": dh, "mask": {"size": window}, "scale": dh ** -0.5, "softcap": 50.0},
+                     "right": {"heads": nh, "dim": dh, "vdim": dh, "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, nh - 1)) for h in range(nh)]},
+                     "left_scale": 0.7, "right_scale": 0.7}}
+    ssm = {"type": "mamba2", "mlp": None, "mixer": {"heads": 2 * H // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}}
+    return {"architecture": "Filasun", "layers": [ssm if i % 3 == 2 else par for i in range(layers)], "logit_softcap": 30.0,
+            "max_positions": d["max_position_embeddings"], "norm": {"eps": 1e-5}, "streams": 4, "vocab": d["vocab_size"], "width": H}
+
+
+def time_design(args, peaks):
+    """Prefill and decode of the Filasun design beside the Qwen2 model of the same layer sizes and layer count (random
+    weights), through the same step function: tokens per second, and per layer the milliseconds behind them."""
+    import torch
+
+    from litinfer_b200.config import config_from_dict
+    from litinfer_b200.models import DecoderModel
+
+    layers = args.layers or 6
+    out = {"only": "design", "layers": layers, "prefill_tokens": args.prefill_tokens, "context": args.context, "rows": []}
+    for shape in args.design_shapes.split(","):
+        for arch in ("filasun", "qwen2"):
+            if arch == "filasun":
+                cfg = filasun_config(shape, layers)
+            else:
+                cfg = bench_config(shape)
+                cfg["num_hidden_layers"] = layers
+            model = DecoderModel.from_random(config_from_dict(cfg).to_model_spec(), 0, "bfloat16", "cuda:0")
+            row = {"shape": shape, "arch": arch, "weights_gb": round(weight_bytes(model) / 1e9, 3)}
+            ms = time_prefill(model, args.prefill_tokens)
+            row["prefill_ms"] = round(ms, 3)
+            row["prefill_tok_s"] = round(args.prefill_tokens / ms * 1e3)
+            for batch in (1, 8, 32):
+                r = time_decode(model, batch, args.context, args.steps, max(args.warmup, 3))
+                row[f"decode_b{batch}_ms"] = round(r["ms_per_step"], 4)
+                row[f"decode_b{batch}_tok_s"] = round(r["tok_s"])
+                # every weight once a step, against the measured copy bandwidth (the cache and the states come on top)
+                row[f"decode_b{batch}_weights_frac"] = round(weight_bytes(model) / (r["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 3)
+            out["rows"].append(row)
+            del model
+            torch.cuda.empty_cache()
+    return out
 
 
 def bench_config(shape: str = "1.5b"):
@@ -656,12 +710,15 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--shape", default="1.5b", choices=sorted(SHAPES), help="layer sizes: the headline 1.5B shape, or the 7B / 14B shapes of the larger workloads")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "mixed", "kernels-decode", "kernels-prefill", "kernels-mixed", "serve", "chunked", "fp32"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "mixed", "kernels-decode", "kernels-prefill", "kernels-mixed", "serve", "chunked", "fp32", "design"],
                     help="measure one part and print a short line (for profiling runs); kernels-*: a table of the "
                          "kernels' device times from torch.profiler; mixed: --batch requests decoding at --context beside "
                          "a portion of --prefill-tokens prompt tokens")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (so that a profiler lists them)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "filasun"],
+                    help="which design the parts behind --only are measured on, with the layer sizes of --shape (default: the headline's Qwen2)")
+    ap.add_argument("--design-shapes", default="1.5b,7b", help="--only design: the shapes whose layer sizes are run, with commas")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -683,11 +740,21 @@ def main() -> int:
     if args.only == "fp32":
         print(json.dumps({"only": "fp32", "shape": args.shape, **fp32_check(cfg)}))
         return 0
+    if args.only == "design":
+        print(json.dumps(time_design(args, load_peaks())))
+        return 0
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
+    if args.arch == "filasun":
+        if args.only == "all":
+            print("bench.py: --arch filasun goes with --only decode|prefill|kernels-decode|kernels-prefill|design")
+            return 2
+        cfg = filasun_config(args.shape, args.layers or 6)
+        cfg["num_hidden_layers"], cfg["max_position_embeddings"] = len(cfg["layers"]), cfg["max_positions"]
+        cfg.update(num_key_value_heads=0, head_dim=0, hidden_size=cfg["width"])
     if args.only in ("decode", "kernels-decode") and args.context + 4096 > cfg["max_position_embeddings"]:
         # a longer context than the shape's own limit, on request: the measurement's model allows it
-        cfg["max_position_embeddings"] = args.context + 4096
+        cfg["max_position_embeddings"] = cfg["max_positions"] = args.context + 4096
     peaks = load_peaks()
     spec = config_from_dict(cfg).to_model_spec()
     model = DecoderModel.from_random(spec, 0, "bfloat16", "cuda:0")
@@ -743,8 +810,8 @@ def main() -> int:
         return 0
     if args.only == "prefill":
         ms = time_prefill(model, args.prefill_tokens, graphs=not args.no_graphs)
-        fl = decode_flops_and_prefill_flops(cfg, args.prefill_tokens)
-        print(json.dumps({"only": "prefill", "tokens": args.prefill_tokens, "graphs": not args.no_graphs, "layers_run": cfg["num_hidden_layers"], "ms": round(ms, 3),
+        fl = decode_flops_and_prefill_flops(cfg, args.prefill_tokens) if args.arch == "qwen2" else 0
+        print(json.dumps({"only": "prefill", "arch": args.arch, "tokens": args.prefill_tokens, "graphs": not args.no_graphs, "layers_run": cfg["num_hidden_layers"], "ms": round(ms, 3),
                           "tok_s": round(args.prefill_tokens / ms * 1e3, 1), "frac": round(fl / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}))
         return 0
 

@@ -20,11 +20,13 @@ int li_attention_generic(const void* qkv, void* out, const void* kcache, const v
 bool li_attention_decode_accepts(int nh, int nkv, int dh, int page_size);
 int li_attention_decode(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                         const int* ctx_lens, const int* old_lens, const int* q_start, int S, int nh, int nkv, int dh, int page_size, int num_pages,
-                        float scale, int window, int max_ctx_len, int expected, cudaStream_t stream);
+                        float scale, int window, int max_ctx_len, int expected, float softcap, const float* slopes, const void* gate,
+                        cudaStream_t stream);
 bool li_attention_prefill_accepts(int nh, int nkv, int dh, int page_size);
 int li_attention_prefill(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size,
-                         int num_pages, float scale, int window, int max_q_len, int skip_single, cudaStream_t stream);
+                         int num_pages, float scale, int window, int max_q_len, int skip_single, float softcap, const float* slopes,
+                         const void* gate, cudaStream_t stream);
 
 bool li_attention_tcgen05_accepts(const void* qkv, const void* kcache, const void* vcache, int nh, int nkv, int dh, int page_size);
 int li_attention_tcgen05(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
@@ -45,9 +47,14 @@ static int validate(int T, int S, int nh, int nkv, int dh, int page_size, int wi
 static int attention_portions(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                               const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
                               float scale, int window, int max_q_len, int max_ctx_len, const int* old_lens, int singles, const int* units,
-                              int slots_portions, int slots_all, bool* done, cudaStream_t stream) {
+                              int slots_portions, int slots_all, float softcap, const float* slopes, const void* gate, bool* done,
+                              cudaStream_t stream) {
     *done = false;
-    const bool tc = max_q_len >= 64 && scale > 0.0f && li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size);
+    // changed scores or outputs (a cap, a distance penalty, a gate per head): the mma.sync tiles and the decode kernel take
+    // them, the tcgen05 tiles do not
+    const bool changed = softcap > 0.0f || slopes != nullptr || gate != nullptr;
+    const bool tc = !changed && max_q_len >= 64 && scale > 0.0f && li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size);
+    if (!tc && scale <= 0.0f) return 0;
     if (!tc && !li_attention_prefill_accepts(nh, nkv, dh, page_size)) return 0;
     const int split = (singles != 0 && max_q_len > 1 && li_attention_decode_accepts(nh, nkv, dh, page_size)) ? 1 : 0;
     // how many sequences the decode kernel will find: the count if it is known, else (a captured step, whose sequences are
@@ -55,14 +62,14 @@ static int attention_portions(const void* qkv, void* out, const void* kcache, co
     const int expected = singles > 0 ? singles : (S + 1) / 2;
     if (split)
         if (int rc = li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, dh,
-                                         page_size, num_pages, scale, window, max_ctx_len, expected, stream))
+                                         page_size, num_pages, scale, window, max_ctx_len, expected, softcap, slopes, gate, stream))
             return rc;
     *done = true;
     if (tc)
         return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
                                     num_pages, scale, window, max_q_len, split, units, split ? slots_portions : slots_all, stream);
     return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
-                                num_pages, scale, window, max_q_len, split, stream);
+                                num_pages, scale, window, max_q_len, split, softcap, slopes, gate, stream);
 }
 
 // singles: how many sequences of the step have one token beside longer ones (0: none; negative: not known, there may be).
@@ -76,15 +83,14 @@ LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache,
                                  float softcap, const float* slopes, const void* gate, cudaStream_t stream) {
     if (int rc = validate(T, S, nh, nkv, dh, page_size, window)) return rc;
     if (T == 0) return 0;
-    const bool changed = softcap > 0.0f || slopes != nullptr || gate != nullptr;      // scores or outputs changed: see attention_generic.cu
-    if (dtype == LI_BF16 && !changed) {
+    if (dtype == LI_BF16) {
         if (max_q_len == 1 && T == S && li_attention_decode_accepts(nh, nkv, dh, page_size))
             return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, nullptr, S, nh, nkv, dh, page_size,
-                                       num_pages, scale, window, max_ctx_len, S, stream);
+                                       num_pages, scale, window, max_ctx_len, S, softcap, slopes, gate, stream);
         bool done = false;
         const int rc = attention_portions(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
                                           num_pages, scale, window, max_q_len, max_ctx_len, old_lens, singles, units, slots_portions, slots_all,
-                                          &done, stream);
+                                          softcap, slopes, gate, &done, stream);
         if (rc || done) return rc;
     }
     return li_attention_generic(qkv, out, kcache, vcache, dtype, block_table, max_blocks, seq_of_token, positions, T, nh, nkv, dh,
@@ -108,13 +114,13 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
     if (which == 0)
         return li_attention_generic(qkv, out, kcache, vcache, dtype, block_table, max_blocks, seq_of_token, positions, T, nh, nkv,
                                     dh, page_size, num_pages, scale, window, softcap, slopes, gate, stream);
-    LI_REQUIRE(softcap <= 0.0f && slopes == nullptr && gate == nullptr, "attention: implementation %d takes no cap, slopes or gate", which);
+    LI_REQUIRE(which != 3 || (softcap <= 0.0f && slopes == nullptr && gate == nullptr), "attention: the tcgen05 kernel takes no cap, slopes or gate");
     LI_REQUIRE(dtype == LI_BF16, "attention: implementation %d takes bfloat16 only", which);
     if (which == 1) {
         LI_REQUIRE(max_q_len == 1 && T == S, "attention: the decode kernel takes one token per sequence");
         LI_REQUIRE(li_attention_decode_accepts(nh, nkv, dh, page_size), "attention: the decode kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
         return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, nullptr, S, nh, nkv, dh, page_size, num_pages,
-                                   scale, window, max_ctx_len, S, stream);
+                                   scale, window, max_ctx_len, S, softcap, slopes, gate, stream);
     }
     if (which == 2 || which == 3) {
         if (which == 2) {
@@ -125,11 +131,12 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
         const int split = (singles != 0 && max_q_len > 1 && li_attention_decode_accepts(nh, nkv, dh, page_size)) ? 1 : 0;
         if (split)
             if (int rc = li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, dh,
-                                             page_size, num_pages, scale, window, max_ctx_len, singles > 0 ? singles : (S + 1) / 2, stream))
+                                             page_size, num_pages, scale, window, max_ctx_len, singles > 0 ? singles : (S + 1) / 2, softcap, slopes,
+                                             gate, stream))
                 return rc;
         if (which == 2)
             return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
-                                        num_pages, scale, window, max_q_len, split, stream);
+                                        num_pages, scale, window, max_q_len, split, softcap, slopes, gate, stream);
         return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
                                     num_pages, scale, window, max_q_len, split, units, split ? slots_portions : slots_all, stream);
     }

@@ -50,31 +50,31 @@ Workspace g_ws[16];
 using namespace attn;
 using namespace attn_decode;
 
-template <int DH, int KB, bool kCut>
+template <int DH, int KB, bool kCut, bool kMod>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ ctx_lens,
                         const int* __restrict__ old_lens, const int* __restrict__ q_start, float* __restrict__ part,
                         unsigned* __restrict__ counters, bf16* __restrict__ out, int nh, int nkv, int page_size, int num_pages,
-                        float scale, int window, int nsplit, int want) {
+                        float scale, int window, int nsplit, int want, ScoreMod mod) {
     extern __shared__ float sm[];
     __shared__ int is_last;
     pdl_launch_dependents();
-    decode_attention_unit<DH, KB, kCut>((int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)threadIdx.x, qkv, kcache, vcache, block_table, max_blocks,
+    decode_attention_unit<DH, KB, kCut, kMod>((int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)threadIdx.x, qkv, kcache, vcache, block_table, max_blocks,
                                   ctx_lens, old_lens, q_start, part, counters, out, nh, nkv, page_size, num_pages, scale, window, nsplit, sm,
-                                  &is_last, [] { __syncthreads(); }, [] { pdl_wait(); }, want);
+                                  &is_last, [] { __syncthreads(); }, [] { pdl_wait(); }, want, mod);
 }
 
 // Many sequences at once: with one CTA per (sequence, kv head) the GPU is already full, and splitting the
 // context over CTAs would only add partial results to write, merge and wait for.  Each of the CTA's warps
 // walks every WARPS-th block of 16 keys with a running softmax; the warps are merged through shared memory in
 // warp order at the end.  The assignment of blocks to warps depends on the sequence alone.
-template <int DH, int WARPS, int KB>
+template <int DH, int WARPS, int KB, bool kMod>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 decode_attention_whole_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                               const int* __restrict__ block_table, int max_blocks, const int* __restrict__ ctx_lens,
                               const int* __restrict__ q_start, bf16* __restrict__ out, int nh, int nkv, int page_size, int num_pages,
-                              float scale, int window) {
+                              float scale, int window, ScoreMod mod) {
     extern __shared__ float sm[];
     pdl_launch_dependents();
     pdl_wait();
@@ -98,9 +98,16 @@ decode_attention_whole_kernel(const bf16* __restrict__ qkv, const bf16* __restri
     const int lo2[2] = {lo, lo}, hi2[2] = {p, p};
     const int* bt = block_table + (size_t)s * max_blocks;
     const int b_first = lo / KB, b_last = p / KB;
+    RowMod rm;
+    if constexpr (kMod) {
+        rm.softcap = mod.softcap;
+        rm.slope[0] = (mod.slopes && g < G) ? mod.slopes[kvh * G + g] : 0.0f;
+        rm.slope[1] = (mod.slopes && g + 8 < G) ? mod.slopes[kvh * G + g + 8] : 0.0f;
+        rm.pos[0] = rm.pos[1] = p;
+    }
 #pragma unroll 1
     for (int b = b_first + warp; b <= b_last; b += WARPS)
-        block_step<DH, KB>(st, qa, kcache, vcache, bt, b * KB, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t);
+        block_step<DH, KB, kMod>(st, qa, kcache, vcache, bt, b * KB, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t, rm);
     const float m0 = st.m[0], m1 = st.m[1];
     const float l0 = quad_sum(st.l[0]), l1 = quad_sum(st.l[1]);
     float* sm_m = sm;
@@ -135,7 +142,10 @@ decode_attention_whole_kernel(const bf16* __restrict__ qkv, const bf16* __restri
             O += sm_o[((size_t)w * G + r) * DH + d] * f;
             L += sm_l[w * 16 + r] * f;
         }
-        out[((size_t)tok * nh + kvh * G + r) * DH + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+        float res = L > 0.0f ? O / L : 0.0f;
+        if constexpr (kMod)
+            if (mod.gate) res *= sigmoid_of(mod.gate[(size_t)tok * nh + kvh * G + r]);
+        out[((size_t)tok * nh + kvh * G + r) * DH + d] = __float2bfloat16_rn(res);
     }
 }
 
@@ -168,10 +178,10 @@ int ensure_workspace(size_t floats, float** buf, unsigned** counters) {
     return 0;
 }
 
-template <int DH>
+template <int DH, bool kMod>
 int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
            const int* ctx_lens, const int* old_lens, const int* q_start, int S, int nh, int nkv, int page_size, int num_pages, float scale,
-           int window, int max_ctx_len, int expected, cudaStream_t stream) {
+           int window, int max_ctx_len, int expected, ScoreMod mod, cudaStream_t stream) {
     const int G = nh / nkv;
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
     // `expected`: how many of the S sequences are this kernel's (a step may hold portions beside them, and a captured step
@@ -197,12 +207,12 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
         if (wsmem <= 200 * 1024) {
             static bool raised = false;
             if (!raised && wsmem > 48 * 1024) {
-                cudaError_t e = cudaFuncSetAttribute(decode_attention_whole_kernel<DH, W, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+                cudaError_t e = cudaFuncSetAttribute(decode_attention_whole_kernel<DH, W, KB, kMod>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
                 if (e != cudaSuccess) return li_fail("attention (decode): cannot raise shared memory: %s", cudaGetErrorString(e));
                 raised = true;
             }
-            li_launch_pdl(decode_attention_whole_kernel<DH, W, KB>, dim3(nkv, S), dim3(W * 32), wsmem, stream, (const bf16*)qkv, (const bf16*)kcache,
-                          (const bf16*)vcache, block_table, max_blocks, ctx_lens, q_start, (bf16*)out, nh, nkv, page_size, num_pages, scale, window);
+            li_launch_pdl(decode_attention_whole_kernel<DH, W, KB, kMod>, dim3(nkv, S), dim3(W * 32), wsmem, stream, (const bf16*)qkv, (const bf16*)kcache,
+                          (const bf16*)vcache, block_table, max_blocks, ctx_lens, q_start, (bf16*)out, nh, nkv, page_size, num_pages, scale, window, mod);
             return li_check_launch("attention (decode, whole context)");
         }
     }
@@ -223,8 +233,8 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     const size_t smem = smem_floats * sizeof(float);
     static bool attr_set = false;
     if (!attr_set && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<DH, KBS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_attention_kernel<DH, KBS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<DH, KBS, false, kMod>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_attention_kernel<DH, KBS, true, kMod>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return li_fail("attention (decode): cannot raise shared memory: %s", cudaGetErrorString(e));
         attr_set = true;
     }
@@ -232,13 +242,13 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
     dim3 grid(nsplit, nkv, S);
     if (cut)
-        li_launch_pdl(decode_attention_kernel<DH, KBS, true>, dim3(grid), dim3(kWarps * 32), smem, stream, (const bf16*)qkv, (const bf16*)kcache,
+        li_launch_pdl(decode_attention_kernel<DH, KBS, true, kMod>, dim3(grid), dim3(kWarps * 32), smem, stream, (const bf16*)qkv, (const bf16*)kcache,
                       (const bf16*)vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, part, counters, (bf16*)out, nh, nkv, page_size,
-                      num_pages, scale, window, nsplit, want);
+                      num_pages, scale, window, nsplit, want, mod);
     else
-        li_launch_pdl(decode_attention_kernel<DH, KBS, false>, dim3(grid), dim3(kWarps * 32), smem, stream, (const bf16*)qkv, (const bf16*)kcache,
+        li_launch_pdl(decode_attention_kernel<DH, KBS, false, kMod>, dim3(grid), dim3(kWarps * 32), smem, stream, (const bf16*)qkv, (const bf16*)kcache,
                       (const bf16*)vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, part, counters, (bf16*)out, nh, nkv, page_size,
-                      num_pages, scale, window, nsplit, 0);
+                      num_pages, scale, window, nsplit, 0, mod);
     return li_check_launch("attention (decode)");
 }
 
@@ -251,11 +261,18 @@ bool li_attention_decode_accepts(int nh, int nkv, int dh, int page_size) {
 
 int li_attention_decode(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                         const int* ctx_lens, const int* old_lens, const int* q_start, int S, int nh, int nkv, int dh, int page_size, int num_pages,
-                        float scale, int window, int max_ctx_len, int expected, cudaStream_t stream) {
+                        float scale, int window, int max_ctx_len, int expected, float softcap, const float* slopes, const void* gate,
+                        cudaStream_t stream) {
+    ScoreMod mod;
+    mod.softcap = softcap;
+    mod.slopes = slopes;
+    mod.gate = (const bf16*)gate;
 #define LI_CASE(D)                                                                                                             \
     case D:                                                                                                                    \
-        return launch<D>(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, page_size, num_pages, scale, \
-                         window, max_ctx_len, expected, stream);
+        return mod.any() ? launch<D, true>(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, page_size, \
+                                           num_pages, scale, window, max_ctx_len, expected, mod, stream)                           \
+                         : launch<D, false>(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, page_size, \
+                                            num_pages, scale, window, max_ctx_len, expected, mod, stream);
     switch (dh) {
         LI_CASE(16) LI_CASE(32) LI_CASE(48) LI_CASE(64) LI_CASE(80) LI_CASE(96) LI_CASE(112) LI_CASE(128) LI_CASE(256)
         default:

@@ -24,10 +24,11 @@ __host__ __device__ inline void split_range(int ctx, int window, int kSplit, int
 
 // One block of KB keys (16: 8-byte loads; 32: 16-byte loads, half as many requests per byte) from the pages of a
 // sequence into the running softmax of a warp.  All loads of the block are issued before the first use.
-template <int DH, int KB>
+template <int DH, int KB, bool kMod = false>
 __device__ __forceinline__ void block_step(RowState<DH>& st, const unsigned (&qa)[DH / 16][4], const bf16* __restrict__ kcache,
                                            const bf16* __restrict__ vcache, const int* __restrict__ bt, int key0, int kvh, int nkv,
-                                           int page_size, int num_pages, const int (&lo2)[2], const int (&hi2)[2], float scale, int g, int t) {
+                                           int page_size, int num_pages, const int (&lo2)[2], const int (&hi2)[2], float scale, int g, int t,
+                                           const attn::RowMod& rm = attn::RowMod{}) {
     if constexpr (KB == 16) {
         int page = bt[key0 / page_size];
         if (page < 0 || page >= num_pages) page = 0;
@@ -36,7 +37,7 @@ __device__ __forceinline__ void block_step(RowState<DH>& st, const unsigned (&qa
         VFrag<DH> vf;
         load_k<DH, true>(kf, kcache + (((size_t)page * nkv + kvh) * page_size + off) * DH, g, t);
         load_v<DH, true>(vf, vcache + ((size_t)page * nkv + kvh) * DH * page_size + off, page_size, g, t);
-        compute16<DH>(st, qa, kf, vf, key0, lo2, hi2, scale, t);
+        compute16<DH, kMod>(st, qa, kf, vf, key0, lo2, hi2, scale, t, rm);
     } else {
         // keys of this thread's key rows: the group of 8 at 8 (g >> 1); of its value columns: the 8 at 8 t.
         // A group of 8 aligned keys lies in one page (pages hold a multiple of 16); groups wholly past the
@@ -49,7 +50,7 @@ __device__ __forceinline__ void block_step(RowState<DH>& st, const unsigned (&qa
         VFrag32<DH> vf;
         load_k32<DH>(kf, kcache + (((size_t)kpage * nkv + kvh) * page_size + kk % page_size) * DH, g, t);
         load_v32<DH>(vf, vcache + ((size_t)vpage * nkv + kvh) * DH * page_size + vk % page_size, page_size, g);
-        compute32<DH>(st, qa, kf, vf, key0, lo2, hi2, scale, t);
+        compute32<DH, kMod>(st, qa, kf, vf, key0, lo2, hi2, scale, t, rm);
     }
 }
 
@@ -66,13 +67,14 @@ __device__ __forceinline__ void block_load32(KFrag32<DH>& kf, VFrag32<DH>& vf, c
     load_v32<DH>(vf, vcache + ((size_t)vpage * nkv + kvh) * DH * page_size + vk % page_size, page_size, g);
 }
 
-template <int DH, int KB, bool kCut = false, typename Sync, typename Wait>
+template <int DH, int KB, bool kCut = false, bool kMod = false, typename Sync, typename Wait>
 __device__ __forceinline__ void decode_attention_unit(int split, int kvh, int s, int tid, const bf16* __restrict__ qkv, const bf16* __restrict__ kcache,
                                                       const bf16* __restrict__ vcache, const int* __restrict__ block_table, int max_blocks,
                                                       const int* __restrict__ ctx_lens, const int* __restrict__ old_lens,
                                                       const int* __restrict__ q_start, float* __restrict__ part, unsigned* __restrict__ counters,
                                                       bf16* __restrict__ out, int nh, int nkv, int page_size, int num_pages, float scale, int window,
-                                                      int nsplit, float* sm, int* is_last, Sync sync, Wait wait_for_queries, int want = 0) {
+                                                      int nsplit, float* sm, int* is_last, Sync sync, Wait wait_for_queries, int want = 0,
+                                                      attn::ScoreMod mod = attn::ScoreMod{}) {
     const int ctx = ctx_lens[s];                           // the step's metadata is in place before its first kernel starts
     // A unit covers KB keys per warp and round.  One round (one round trip to memory) where the units of all sequences
     // fit the GPU at once (want = 0).  Else the sequence's own context is cut into `want` units of as many rounds as that
@@ -121,12 +123,19 @@ __device__ __forceinline__ void decode_attention_unit(int split, int kvh, int s,
     RowState<DH> st;
     st.init();
     const int lo2[2] = {lo, lo}, hi2[2] = {k_end - 1, k_end - 1};
+    attn::RowMod rm;
+    if constexpr (kMod) {
+        rm.softcap = mod.softcap;
+        rm.slope[0] = (mod.slopes && g < G) ? mod.slopes[kvh * G + g] : 0.0f;
+        rm.slope[1] = (mod.slopes && g + 8 < G) ? mod.slopes[kvh * G + g + 8] : 0.0f;
+        rm.pos[0] = rm.pos[1] = p;
+    }
     if (my_block) {
         if constexpr (KB == 32) {
             if (!early) block_load32<DH>(kf_early, vf_early, kcache, vcache, bt, my_key0, k_end - 1, kvh, nkv, page_size, num_pages, g, t);
-            compute32<DH>(st, qa, kf_early, vf_early, my_key0, lo2, hi2, scale, t);
+            compute32<DH, kMod>(st, qa, kf_early, vf_early, my_key0, lo2, hi2, scale, t, rm);
         } else {
-            block_step<DH, KB>(st, qa, kcache, vcache, bt, my_key0, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t);
+            block_step<DH, KB, kMod>(st, qa, kcache, vcache, bt, my_key0, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t, rm);
         }
     }
     if constexpr (kCut) {
@@ -134,7 +143,7 @@ __device__ __forceinline__ void decode_attention_unit(int split, int kvh, int s,
         for (int rd = 1; rd < rounds; ++rd) {
             const int key0 = k_begin + (rd * kWarps + warp) * KB;
             if (key0 < k_end && key0 + KB > lo)            // warp-uniform
-                block_step<DH, KB>(st, qa, kcache, vcache, bt, key0, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t);
+                block_step<DH, KB, kMod>(st, qa, kcache, vcache, bt, key0, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t, rm);
         }
     }
     const float m0 = st.m[0], m1 = st.m[1];
@@ -253,7 +262,10 @@ __device__ __forceinline__ void decode_attention_unit(int split, int kvh, int s,
             if (e < G * DH) {
                 const int r = e / DH, d = e - r * DH;
                 const float L = l_sm[r];
-                out[((size_t)tok * nh + kvh * G + r) * DH + d] = __float2bfloat16_rn(L > 0.0f ? O[q] / L : 0.0f);
+                float res = L > 0.0f ? O[q] / L : 0.0f;
+                if constexpr (kMod)
+                    if (mod.gate) res *= attn::sigmoid_of(mod.gate[(size_t)tok * nh + kvh * G + r]);
+                out[((size_t)tok * nh + kvh * G + r) * DH + d] = __float2bfloat16_rn(res);
             }
         }
     }

@@ -21,6 +21,37 @@
 
 namespace attn {
 
+// Optional changes of the scores and of the output (see attention_generic.cu): a cap softcap * tanh(s / softcap) after
+// the scale, slopes[h] * (p - key) taken off, and the head's output times sigmoid(gate[token, h]).  All off when zero.
+struct ScoreMod {
+    float softcap = 0.0f;
+    const float* slopes = nullptr;
+    const bf16* gate = nullptr;
+    bool any() const { return softcap > 0.0f || slopes != nullptr || gate != nullptr; }
+};
+
+// tanh from the fast exponential and reciprocal (relative error about 1e-6): 1 - 2 / (1 + e^(2x)).
+__device__ __forceinline__ float tanh_fast(float x) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));
+    return 1.0f - __fdividef(2.0f, 1.0f + e);
+}
+
+// The score of a key at `dist` positions behind its query, from the scaled dot product.
+__device__ __forceinline__ float changed_score(float s, float softcap, float slope, int dist) {
+    if (softcap > 0.0f) s = softcap * tanh_fast(__fdividef(s, softcap));
+    return fmaf(-slope, (float)dist, s);
+}
+
+__device__ __forceinline__ float sigmoid_of(bf16 g) { return 1.0f / (1.0f + expf(-__bfloat162float(g))); }
+
+// The same for the two rows a thread sees in a tile of 16 rows: their slopes and the position of their query.
+struct RowMod {
+    float softcap = 0.0f;
+    float slope[2] = {0.0f, 0.0f};
+    int pos[2] = {0, 0};
+};
+
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -113,9 +144,9 @@ __device__ __forceinline__ void load_v(VFrag<DH>& v, const bf16* vbase, int page
 
 // 16 rows against the 16 keys whose fragments are given; key0 is the absolute position of the
 // block's first key.  A key is visible to row r iff lo[r] <= key <= hi[r].
-template <int DH>
+template <int DH, bool kMod = false>
 __device__ __forceinline__ void compute16(RowState<DH>& st, const unsigned (&qa)[DH / 16][4], const KFrag<DH>& kf, const VFrag<DH>& vf,
-                                          int key0, const int (&lo)[2], const int (&hi)[2], float scale, int t) {
+                                          int key0, const int (&lo)[2], const int (&hi)[2], float scale, int t, const RowMod& rm = RowMod{}) {
     constexpr int KS = DH / 16, NT = DH / 8;
     const uint2* kb0 = kf.t0;
     const uint2* kb1 = kf.t1;
@@ -132,10 +163,17 @@ __device__ __forceinline__ void compute16(RowState<DH>& st, const unsigned (&qa)
     float alpha[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        const float v0 = (kk >= lo[r] && kk <= hi[r]) ? s0[2 * r] * scale : -INFINITY;
-        const float v1 = (kk + 1 >= lo[r] && kk + 1 <= hi[r]) ? s0[2 * r + 1] * scale : -INFINITY;
-        const float v2 = (kk + 2 >= lo[r] && kk + 2 <= hi[r]) ? s1[2 * r] * scale : -INFINITY;
-        const float v3 = (kk + 3 >= lo[r] && kk + 3 <= hi[r]) ? s1[2 * r + 1] * scale : -INFINITY;
+        float w0 = s0[2 * r] * scale, w1 = s0[2 * r + 1] * scale, w2 = s1[2 * r] * scale, w3 = s1[2 * r + 1] * scale;
+        if constexpr (kMod) {
+            w0 = changed_score(w0, rm.softcap, rm.slope[r], rm.pos[r] - kk);
+            w1 = changed_score(w1, rm.softcap, rm.slope[r], rm.pos[r] - kk - 1);
+            w2 = changed_score(w2, rm.softcap, rm.slope[r], rm.pos[r] - kk - 2);
+            w3 = changed_score(w3, rm.softcap, rm.slope[r], rm.pos[r] - kk - 3);
+        }
+        const float v0 = (kk >= lo[r] && kk <= hi[r]) ? w0 : -INFINITY;
+        const float v1 = (kk + 1 >= lo[r] && kk + 1 <= hi[r]) ? w1 : -INFINITY;
+        const float v2 = (kk + 2 >= lo[r] && kk + 2 <= hi[r]) ? w2 : -INFINITY;
+        const float v3 = (kk + 3 >= lo[r] && kk + 3 <= hi[r]) ? w3 : -INFINITY;
         const float mx = quad_max(fmaxf(fmaxf(v0, v1), fmaxf(v2, v3)));
         const float mn = fmaxf(st.m[r], mx);
         const float ms = (mn == -INFINITY) ? 0.0f : mn;         // nothing visible yet: keep everything at zero
@@ -214,9 +252,9 @@ __device__ __forceinline__ void load_v32(VFrag32<DH>& vf, const bf16* vkeys, int
     for (int j = 0; j < DH / 8; ++j) vf.v[j] = ld16_stream(vkeys + (size_t)(j * 8 + g) * page_size);
 }
 
-template <int DH>
+template <int DH, bool kMod = false>
 __device__ __forceinline__ void compute32(RowState<DH>& st, const unsigned (&qa)[DH / 16][4], const KFrag32<DH>& kf, const VFrag32<DH>& vf,
-                                          int key0, const int (&lo)[2], const int (&hi)[2], float scale, int t) {
+                                          int key0, const int (&lo)[2], const int (&hi)[2], float scale, int t, const RowMod& rm = RowMod{}) {
     constexpr int F = DH / 32, R = (DH % 32) / 16, NT = DH / 8;
     float sc[4][4];
 #pragma unroll
@@ -239,7 +277,9 @@ __device__ __forceinline__ void compute32(RowState<DH>& st, const unsigned (&qa)
             for (int e = 0; e < 2; ++e) {
                 const int key = key0 + 8 * t + 4 * (tau >> 1) + 2 * (tau & 1) + e;
                 float& v = sc[tau][2 * r + e];
-                v = (key >= lo[r] && key <= hi[r]) ? v * scale : -INFINITY;
+                float w = v * scale;
+                if constexpr (kMod) w = changed_score(w, rm.softcap, rm.slope[r], rm.pos[r] - key);
+                v = (key >= lo[r] && key <= hi[r]) ? w : -INFINITY;
                 mx = fmaxf(mx, v);
             }
         }

@@ -62,12 +62,12 @@ __device__ __forceinline__ int tile_key(int tau, int n) {
     return 8 * (n >> 1) + 4 * (s & 1) + 32 * (s >> 1) + 2 * h + (n & 1);
 }
 
-template <int DH>
+template <int DH, bool kMod>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, const bf16* __restrict__ kcache,
                          const bf16* __restrict__ vcache, const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ q_start, const int* __restrict__ ctx_lens, int nh, int nkv, int page_size,
-                         int num_pages, float scale, int window, int skip_single) {
+                         int num_pages, float scale, int window, int skip_single, attn::ScoreMod mod) {
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int KCH = DH / 8;                     // 16-byte chunks in a key row
     constexpr int kKBytes = kKeys * DH * 2, kVBytes = DH * kKeys * 2;
@@ -121,7 +121,10 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, c
     const int warp_p_last = warp_p_first + min(16, n - i0) - 1;
     const int warp_key_lo = (window > 0 && warp_p_first - window + 1 > 0) ? warp_p_first - window + 1 : 0;
     const int warp_lo_max = (window > 0 && warp_p_last - window + 1 > 0) ? warp_p_last - window + 1 : 0;     // the largest lower bound among the warp's rows
-    const float scale_log2 = scale * 1.4426950408889634f;
+    // kMod: the scores are changed (cap, distance penalty) before the softmax; they are then brought to base-2 units at
+    // once and the factor below is 1
+    const float scale_log2 = kMod ? 1.0f : scale * 1.4426950408889634f;
+    [[maybe_unused]] const float slope = (kMod && mod.slopes) ? mod.slopes[h] : 0.0f;
 
     const int* bt = block_table + (size_t)s * max_blocks;
     auto page_of = [&](int key) {
@@ -192,6 +195,18 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, c
             // keys in base 2: exp(x scale - m) = 2^(x c - m'), c = scale log2(e), m' kept in the scaled units.
             // Rows g (index 0: c0, c1) and g + 8 (index 1: c2, c3).
             const bool interior = (k0 + kKeys - 1 <= warp_p_first) && (k0 >= warp_lo_max);
+            if constexpr (kMod) {
+#pragma unroll
+                for (int r = 0; r < 2; ++r)
+#pragma unroll
+                    for (int tau = 0; tau < 8; ++tau)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int key = k0 + tile_key(tau, 2 * t + e);
+                            float& v = sc[tau][2 * r + e];
+                            v = attn::changed_score(v * scale, mod.softcap, slope, hi[r] - key) * 1.4426950408889634f;
+                        }
+            }
             float alpha[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
@@ -254,7 +269,13 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, c
     }
     if (!warp_active) return;
     const float l0 = quad_sum(st.l[0]), l1 = quad_sum(st.l[1]);
-    const float inv0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, inv1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+    float inv0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, inv1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+    if constexpr (kMod) {
+        if (mod.gate) {
+            if (r_lo < n) inv0 *= attn::sigmoid_of(mod.gate[(size_t)(tok0 + r_lo) * nh + h]);
+            if (r_hi < n) inv1 *= attn::sigmoid_of(mod.gate[(size_t)(tok0 + r_hi) * nh + h]);
+        }
+    }
     bf16* o_lo = out + (size_t)(tok0 + r_lo) * nh * DH + (size_t)h * DH;
     bf16* o_hi = out + (size_t)(tok0 + r_hi) * nh * DH + (size_t)h * DH;
 #pragma unroll
@@ -265,22 +286,22 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, c
     }
 }
 
-template <int DH>
+template <int DH, bool kMod>
 int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
            const int* q_start, const int* ctx_lens, int S, int nh, int nkv, int page_size, int num_pages, float scale, int window,
-           int max_q_len, int skip_single, cudaStream_t stream) {
+           int max_q_len, int skip_single, attn::ScoreMod mod, cudaStream_t stream) {
     LI_REQUIRE(S <= 65535 && ceil_div(max_q_len > 0 ? max_q_len : 1, kTile) <= 65535, "attention (prefill): batch %d or portions of %d tokens too large for one launch", S, max_q_len);
     constexpr size_t smem = 2 * (size_t)(kKeys * DH * 2 + DH * kKeys * 2);
     static bool raised = false;
     if (!raised && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<DH, kMod>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return li_fail("attention (prefill): cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
         raised = true;
     }
     dim3 grid(nh, ceil_div(max_q_len > 0 ? max_q_len : 1, kTile), S);
-    prefill_attention_kernel<DH><<<grid, kWarps * 32, smem, stream>>>((const bf16*)qkv, (bf16*)out, (const bf16*)kcache,
-                                                                      (const bf16*)vcache, block_table, max_blocks, q_start, ctx_lens,
-                                                                      nh, nkv, page_size, num_pages, scale, window, skip_single);
+    prefill_attention_kernel<DH, kMod><<<grid, kWarps * 32, smem, stream>>>((const bf16*)qkv, (bf16*)out, (const bf16*)kcache,
+                                                                            (const bf16*)vcache, block_table, max_blocks, q_start, ctx_lens,
+                                                                            nh, nkv, page_size, num_pages, scale, window, skip_single, mod);
     return li_check_launch("attention (prefill)");
 }
 
@@ -293,13 +314,20 @@ bool li_attention_prefill_accepts(int nh, int nkv, int dh, int page_size) {
 
 int li_attention_prefill(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size,
-                         int num_pages, float scale, int window, int max_q_len, int skip_single, cudaStream_t stream) {
+                         int num_pages, float scale, int window, int max_q_len, int skip_single, float softcap, const float* slopes,
+                         const void* gate, cudaStream_t stream) {
     (void)T;
+    attn::ScoreMod mod;
+    mod.softcap = softcap;
+    mod.slopes = slopes;
+    mod.gate = (const bf16*)gate;
     LI_REQUIRE(scale > 0.0f, "attention (prefill): the scale must be positive, got %g", (double)scale);
 #define LI_CASE(D)                                                                                                                  \
     case D:                                                                                                                         \
-        return launch<D>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, S, nh, nkv, page_size, num_pages, scale, \
-                         window, max_q_len, skip_single, stream);
+        return mod.any() ? launch<D, true>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, S, nh, nkv, page_size,  \
+                                           num_pages, scale, window, max_q_len, skip_single, mod, stream)                                 \
+                         : launch<D, false>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, S, nh, nkv, page_size, \
+                                            num_pages, scale, window, max_q_len, skip_single, mod, stream);
     switch (dh) {
         LI_CASE(16) LI_CASE(32) LI_CASE(48) LI_CASE(64) LI_CASE(80) LI_CASE(96) LI_CASE(112) LI_CASE(128) LI_CASE(256)
         default:

@@ -131,13 +131,13 @@ int li_conv_state_shift(const void* in, int dtype, int in_stride, int in_off, fl
     const int* q_start, const int* slots, int S, int C, int taps, cudaStream_t stream);
 
 /* Per head S [N, P]: S = exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x, dt = softplus(dt_raw + dt_bias); xbc
- * [T, C] holds x | B | C; a sequence's tokens in order, its state read and written once. */
+ * [T, C] holds x | B | C; a sequence's tokens in order, its state read and written once (kept as [heads][P][N]). */
 int li_ssm_scan(const void* xbc, int dtype, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log,
     const float* D, float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads,
     int P, int N, int groups, cudaStream_t stream);
 
 /* Per head S [d, dv]: S = decay S + k v^T, out = S^T q, with q, k, v = silu of the columns at q_off, k_off, v_off
- * of qkv [T, stride]. */
+ * of qkv [T, stride]; the state is kept as [heads][dv][d]. */
 int li_decay_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const float* decay, float* state,
     long long state_stride, const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv,
     cudaStream_t stream);

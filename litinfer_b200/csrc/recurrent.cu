@@ -2,8 +2,8 @@
 //
 // Every kernel here finds a sequence's tokens through q_start[s] .. q_start[s + 1] and its state through
 // state_slots[s], both on the device, so a step of single tokens launches the same grid whatever the slots hold and can
-// be replayed from a captured graph.  A sequence's tokens are walked in order inside one block; the state is read once,
-// kept in shared memory and written once.  State, decays, step sizes, gates of the recurrence and every sum are float;
+// be replayed from a captured graph.  A sequence's tokens are walked in order; the state is read once, kept in registers
+// and written once.  State, decays, step sizes, gates of the recurrence and every sum are float;
 // the projections come in the run dtype.
 //
 //   * li_causal_conv_silu / li_conv_state_shift: a depthwise causal convolution over the last `taps` inputs of each
@@ -73,90 +73,158 @@ __global__ void conv_state_shift_kernel(const T* __restrict__ in, int in_stride,
         if (j < taps - 1) st[(size_t)j * C + c] = keep[j];
 }
 
-// One block per (head, sequence), a thread per column of the head's state.
-// xbc [T, C]: x (heads * P) | B (groups * N) | C (groups * N), after convolution and activation.
-template <typename T>
-__global__ void ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, int dt_stride, const float* __restrict__ dt_bias,
-                                const float* __restrict__ A_log, const float* __restrict__ D, float* __restrict__ state, long long state_stride,
-                                const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ y, int heads, int P, int N,
-                                int groups) {
-    extern __shared__ float smem[];
-    float* S = smem;                       // [N][P]
-    float* bc = smem + (size_t)N * P;      // two buffers of B [N] | C [N]
-    pdl_launch_dependents();
-    pdl_wait();
-    const int h = blockIdx.x, s = blockIdx.y, c = threadIdx.x;
-    const int q0 = q_start[s], q1 = q_start[s + 1];
-    if (q1 <= q0) return;
-    const int g = h / (heads / groups);
-    const int inner = heads * P;
-    float* st = state + (size_t)slots[s] * state_stride + (size_t)h * N * P;
-    for (int i = c; i < N * P; i += blockDim.x) S[i] = st[i];
-    const float rate = expf(A_log[h]), bias = dt_bias[h], skip = D[h];
-    for (int t = q0; t < q1; ++t) {
-        float* buf = bc + (size_t)((t - q0) & 1) * 2 * N;
-        const T* row = xbc + (size_t)t * C;
-        for (int n = c; n < N; n += blockDim.x) {
-            buf[n] = to_float(row[inner + g * N + n]);
-            buf[N + n] = to_float(row[inner + (groups + g) * N + n]);
-        }
-        __syncthreads();
-        if (c < P) {
-            const float dt = softplus_f(to_float(dt_raw[(size_t)t * dt_stride + h]) + bias);
-            const float decay = expf(-rate * dt);
-            const float x = to_float(row[h * P + c]);
-            const float dx = dt * x;
-            float acc = 0.0f;
-            for (int n = 0; n < N; ++n) {
-                const float v = fmaf(decay, S[n * P + c], buf[n] * dx);
-                S[n * P + c] = v;
-                acc = fmaf(v, buf[N + n], acc);
-            }
-            y[(size_t)t * inner + h * P + c] = fmaf(skip, x, acc);
-        }
-    }
-    __syncthreads();
-    for (int i = c; i < N * P; i += blockDim.x) st[i] = S[i];
+// The two recurrences walk a sequence's tokens in order, but every column of a head's state moves on by itself:
+// S[:, c] <- a_t S[:, c] + w_t[:] u_t[c],  out_t[c] = sum_i S[i, c] r_t[i].  So a column is the unit of work: eight lanes
+// hold it in registers (element i with lane i % 8), four columns share a warp, four warps a block; a block stages the
+// vectors of kStage tokens that all its columns need (w, r, and the scalars) in shared memory once, with the
+// activations applied, and the columns then run through them with three shuffles a token for the sum.  The state is
+// stored column by column ([head][column][element]) so that it is read and written in whole lines.
+constexpr int kStage = 16;          // tokens staged at a time
+constexpr int kColWarps = 4;        // warps a block
+constexpr int kCols = kColWarps * 4;
+
+__device__ __forceinline__ float oct_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v + __shfl_xor_sync(0xffffffffu, v, 4);
 }
 
-// One block per (head, sequence), a thread per column of the head's state.
-// q, k [T, stride] at columns q_off + h d, k_off + h d; v at v_off + h dv; all before their activation.
-template <typename T>
-__global__ void decay_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int v_off, const float* __restrict__ decay,
-                                  float* __restrict__ state, long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots,
-                                  float* __restrict__ out, int heads, int d, int dv) {
+// xbc [T, C]: x (heads * P) | B (groups * N) | C (groups * N), after convolution and activation.  R = ceil(N / 8).
+template <typename T, int R>
+__global__ void __launch_bounds__(kColWarps * 32)
+ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, int dt_stride, const float* __restrict__ dt_bias,
+                const float* __restrict__ A_log, const float* __restrict__ D, float* __restrict__ state, long long state_stride,
+                const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ y, int heads, int P, int N, int groups) {
     extern __shared__ float smem[];
-    float* S = smem;                       // [d][dv]
-    float* qk = smem + (size_t)d * dv;     // two buffers of q [d] | k [d]
+    float* Bs = smem;                           // [kStage][N]
+    float* Cs = Bs + (size_t)kStage * N;        // [kStage][N]
+    float* xs = Cs + (size_t)kStage * N;        // [kStage][kCols]
+    float* dts = xs + kStage * kCols;           // [kStage] step size
+    float* das = dts + kStage;                  // [kStage] decay
     pdl_launch_dependents();
     pdl_wait();
-    const int h = blockIdx.x, s = blockIdx.y, c = threadIdx.x;
+    const int h = blockIdx.y, s = blockIdx.z;
     const int q0 = q_start[s], q1 = q_start[s + 1];
     if (q1 <= q0) return;
-    float* st = state + (size_t)slots[s] * state_stride + (size_t)h * d * dv;
-    for (int i = c; i < d * dv; i += blockDim.x) S[i] = st[i];
-    const float lam = decay[h];
-    for (int t = q0; t < q1; ++t) {
-        float* buf = qk + (size_t)((t - q0) & 1) * 2 * d;
-        const T* row = qkv + (size_t)t * stride;
-        for (int i = c; i < d; i += blockDim.x) {
-            buf[i] = silu_f(to_float(row[q_off + h * d + i]));
-            buf[d + i] = silu_f(to_float(row[k_off + h * d + i]));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int m = lane & 7;
+    const int col0 = blockIdx.x * kCols;
+    const int c = col0 + warp * 4 + (lane >> 3);          // this lane's column of the head
+    const bool live = c < P;
+    const int g = h / (heads / groups);
+    const int inner = heads * P;
+    float* st = state + (size_t)slots[s] * state_stride + ((size_t)h * P + (live ? c : 0)) * N;
+    float S[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) S[k] = (live && m + 8 * k < N) ? st[m + 8 * k] : 0.0f;
+    const float rate = expf(A_log[h]), bias = dt_bias[h], skip = D[h];
+    for (int t0 = q0; t0 < q1; t0 += kStage) {
+        const int nt = min(kStage, q1 - t0);
+        __syncthreads();                                   // the stage before has been used up
+        for (int e = threadIdx.x; e < nt * N; e += blockDim.x) {
+            const int tk = e / N, n = e - tk * N;
+            const T* row = xbc + (size_t)(t0 + tk) * C;
+            Bs[tk * N + n] = to_float(row[inner + g * N + n]);
+            Cs[tk * N + n] = to_float(row[inner + (groups + g) * N + n]);
+        }
+        for (int e = threadIdx.x; e < nt * kCols; e += blockDim.x) {
+            const int tk = e / kCols, j = e - tk * kCols;
+            xs[e] = col0 + j < P ? to_float(xbc[(size_t)(t0 + tk) * C + h * P + col0 + j]) : 0.0f;
+        }
+        if (threadIdx.x < nt) {
+            const float dt = softplus_f(to_float(dt_raw[(size_t)(t0 + threadIdx.x) * dt_stride + h]) + bias);
+            dts[threadIdx.x] = dt;
+            das[threadIdx.x] = expf(-rate * dt);
         }
         __syncthreads();
-        if (c < dv) {
-            const float v = silu_f(to_float(row[v_off + h * dv + c]));
+#pragma unroll 4
+        for (int tk = 0; tk < nt; ++tk) {
+            const float x = xs[tk * kCols + warp * 4 + (lane >> 3)];
+            const float dx = dts[tk] * x, decay = das[tk];
+            const float* b = Bs + tk * N;
+            const float* cc = Cs + tk * N;
             float acc = 0.0f;
-            for (int i = 0; i < d; ++i) {
-                const float sv = fmaf(lam, S[i * dv + c], buf[d + i] * v);
-                S[i * dv + c] = sv;
-                acc = fmaf(sv, buf[i], acc);
+#pragma unroll
+            for (int k = 0; k < R; ++k) {
+                const int n = m + 8 * k;
+                if (n < N) {
+                    S[k] = fmaf(decay, S[k], b[n] * dx);
+                    acc = fmaf(S[k], cc[n], acc);
+                }
             }
-            out[(size_t)t * heads * dv + h * dv + c] = acc;
+            acc = oct_sum(acc);
+            if (live && m == 0) y[(size_t)(t0 + tk) * inner + h * P + c] = fmaf(skip, x, acc);
         }
     }
-    __syncthreads();
-    for (int i = c; i < d * dv; i += blockDim.x) st[i] = S[i];
+    if (live) {
+#pragma unroll
+        for (int k = 0; k < R; ++k)
+            if (m + 8 * k < N) st[m + 8 * k] = S[k];
+    }
+}
+
+// q, k [T, stride] at columns q_off + h d, k_off + h d; v at v_off + h dv; all before their activation.  R = ceil(d / 8).
+template <typename T, int R>
+__global__ void __launch_bounds__(kColWarps * 32)
+decay_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int v_off, const float* __restrict__ decay,
+                  float* __restrict__ state, long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots,
+                  float* __restrict__ out, int heads, int d, int dv) {
+    extern __shared__ float smem[];
+    float* qs = smem;                           // [kStage][d]
+    float* ks = qs + (size_t)kStage * d;        // [kStage][d]
+    float* vs = ks + (size_t)kStage * d;        // [kStage][kCols]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.y, s = blockIdx.z;
+    const int q0 = q_start[s], q1 = q_start[s + 1];
+    if (q1 <= q0) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int m = lane & 7;
+    const int col0 = blockIdx.x * kCols;
+    const int c = col0 + warp * 4 + (lane >> 3);
+    const bool live = c < dv;
+    float* st = state + (size_t)slots[s] * state_stride + ((size_t)h * dv + (live ? c : 0)) * d;
+    float S[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) S[k] = (live && m + 8 * k < d) ? st[m + 8 * k] : 0.0f;
+    const float lam = decay[h];
+    for (int t0 = q0; t0 < q1; t0 += kStage) {
+        const int nt = min(kStage, q1 - t0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < nt * d; e += blockDim.x) {
+            const int tk = e / d, i = e - tk * d;
+            const T* row = qkv + (size_t)(t0 + tk) * stride;
+            qs[tk * d + i] = silu_f(to_float(row[q_off + h * d + i]));
+            ks[tk * d + i] = silu_f(to_float(row[k_off + h * d + i]));
+        }
+        for (int e = threadIdx.x; e < nt * kCols; e += blockDim.x) {
+            const int tk = e / kCols, j = e - tk * kCols;
+            vs[e] = col0 + j < dv ? silu_f(to_float(qkv[(size_t)(t0 + tk) * stride + v_off + h * dv + col0 + j])) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int tk = 0; tk < nt; ++tk) {
+            const float v = vs[tk * kCols + warp * 4 + (lane >> 3)];
+            const float* kk = ks + tk * d;
+            const float* qq = qs + tk * d;
+            float acc = 0.0f;
+#pragma unroll
+            for (int k = 0; k < R; ++k) {
+                const int i = m + 8 * k;
+                if (i < d) {
+                    S[k] = fmaf(lam, S[k], kk[i] * v);
+                    acc = fmaf(S[k], qq[i], acc);
+                }
+            }
+            acc = oct_sum(acc);
+            if (live && m == 0) out[(size_t)(t0 + tk) * heads * dv + h * dv + c] = acc;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int k = 0; k < R; ++k)
+            if (m + 8 * k < d) st[m + 8 * k] = S[k];
+    }
 }
 
 // One block per (token, group).  mode 0: v = y silu(z), out = v rinv w; mode 1: out = y rinv w sigmoid(z).
@@ -187,8 +255,6 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ y, const T* __res
         o[j] = from_float<T>(v);
     }
 }
-
-int round_up_warp(int n) { return (n + 31) / 32 * 32; }
 
 }  // namespace
 
@@ -232,56 +298,71 @@ LI_EXPORT int li_conv_state_shift(const void* in, int dtype, int in_stride, int 
     return li_check_launch("conv_state_shift");
 }
 
-LI_EXPORT int li_ssm_scan(const void* xbc, int dtype, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log,
-                          const float* D, float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads,
-                          int P, int N, int groups, cudaStream_t stream) {
-    LI_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0, "state-space scan: %d heads in %d groups", heads, groups);
-    LI_REQUIRE(P > 0 && P <= 1024 && N > 0, "state-space scan: head size %d, state size %d", P, N);
-    LI_REQUIRE(C == heads * P + 2 * groups * N, "state-space scan: %d channels for %d heads of %d and %d groups of %d", C, heads, P, groups, N);
-    if (S == 0) return 0;
-    LI_REQUIRE(S <= 65535, "state-space scan: %d sequences in one launch", S);
-    const size_t smem = ((size_t)N * P + 4 * (size_t)N) * sizeof(float);
-    LI_REQUIRE(smem <= 200 * 1024, "state-space scan: a state of %d x %d does not fit shared memory", N, P);
-    const dim3 grid(heads, S), block(round_up_warp(P));
-    cudaError_t e;
-    if (dtype == LI_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = li_launch_pdl(ssm_scan_kernel<float>, grid, block, smem, stream, (const float*)xbc, C, (const float*)dt_raw, dt_stride, dt_bias, A_log, D, state,
-                          state_stride, q_start, slots, y, heads, P, N, groups);
-    } else if (dtype == LI_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = li_launch_pdl(ssm_scan_kernel<bf16>, grid, block, smem, stream, (const bf16*)xbc, C, (const bf16*)dt_raw, dt_stride, dt_bias, A_log, D, state,
-                          state_stride, q_start, slots, y, heads, P, N, groups);
-    } else {
-        return li_fail("state-space scan: unknown dtype %d", dtype);
-    }
+template <typename T, int R>
+static int launch_ssm(const void* xbc, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log, const float* D,
+                      float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads, int P, int N,
+                      int groups, cudaStream_t stream) {
+    const size_t smem = ((size_t)2 * kStage * N + kStage * kCols + 2 * kStage) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = li_launch_pdl(ssm_scan_kernel<T, R>, dim3(ceil_div(P, kCols), heads, S), dim3(kColWarps * 32), smem, stream, (const T*)xbc, C,
+                                  (const T*)dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, heads, P, N, groups);
     if (e != cudaSuccess) return li_fail("ssm_scan: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("ssm_scan");
 }
 
+// The state of a slot: [heads][P][N] (a column of the head's N x P matrix at a time).
+LI_EXPORT int li_ssm_scan(const void* xbc, int dtype, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log,
+                          const float* D, float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads,
+                          int P, int N, int groups, cudaStream_t stream) {
+    LI_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0, "state-space scan: %d heads in %d groups", heads, groups);
+    LI_REQUIRE(P > 0 && N > 0 && N <= 256, "state-space scan: head size %d, state size %d (at most 256)", P, N);
+    LI_REQUIRE(C == heads * P + 2 * groups * N, "state-space scan: %d channels for %d heads of %d and %d groups of %d", C, heads, P, groups, N);
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "state-space scan: unknown dtype %d", dtype);
+    if (S == 0) return 0;
+    LI_REQUIRE(S <= 65535 && heads <= 65535, "state-space scan: %d sequences or %d heads in one launch", S, heads);
+#define LI_SCAN(RR)                                                                                                                            \
+    return dtype == LI_F32 ? launch_ssm<float, RR>(xbc, C, dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, S, heads, \
+                                                   P, N, groups, stream)                                                                       \
+                           : launch_ssm<bf16, RR>(xbc, C, dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, S, heads,  \
+                                                  P, N, groups, stream)
+    if (N <= 16) { LI_SCAN(2); }
+    if (N <= 32) { LI_SCAN(4); }
+    if (N <= 64) { LI_SCAN(8); }
+    if (N <= 128) { LI_SCAN(16); }
+    LI_SCAN(32);
+#undef LI_SCAN
+}
+
+template <typename T, int R>
+static int launch_decay(const void* qkv, int stride, int q_off, int k_off, int v_off, const float* decay, float* state, long long state_stride,
+                        const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv, cudaStream_t stream) {
+    const size_t smem = ((size_t)2 * kStage * d + kStage * kCols) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = li_launch_pdl(decay_scan_kernel<T, R>, dim3(ceil_div(dv, kCols), heads, S), dim3(kColWarps * 32), smem, stream, (const T*)qkv, stride,
+                                  q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, heads, d, dv);
+    if (e != cudaSuccess) return li_fail("decay_scan: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("decay_scan");
+}
+
+// The state of a slot: [heads][dv][d] (a column of the head's d x dv matrix at a time).
 LI_EXPORT int li_decay_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const float* decay, float* state,
                             long long state_stride, const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv,
                             cudaStream_t stream) {
-    LI_REQUIRE(heads > 0 && d > 0 && dv > 0 && dv <= 1024, "decay scan: %d heads of %d x %d", heads, d, dv);
+    LI_REQUIRE(heads > 0 && d > 0 && d <= 256 && dv > 0, "decay scan: %d heads of %d x %d (keys of at most 256)", heads, d, dv);
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "decay scan: unknown dtype %d", dtype);
     if (S == 0) return 0;
-    LI_REQUIRE(S <= 65535, "decay scan: %d sequences in one launch", S);
-    const size_t smem = ((size_t)d * dv + 4 * (size_t)d) * sizeof(float);
-    LI_REQUIRE(smem <= 200 * 1024, "decay scan: a state of %d x %d does not fit shared memory", d, dv);
-    const dim3 grid(heads, S), block(round_up_warp(dv));
-    cudaError_t e;
-    if (dtype == LI_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = li_launch_pdl(decay_scan_kernel<float>, grid, block, smem, stream, (const float*)qkv, stride, q_off, k_off, v_off, decay, state, state_stride,
-                          q_start, slots, out, heads, d, dv);
-    } else if (dtype == LI_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = li_launch_pdl(decay_scan_kernel<bf16>, grid, block, smem, stream, (const bf16*)qkv, stride, q_off, k_off, v_off, decay, state, state_stride,
-                          q_start, slots, out, heads, d, dv);
-    } else {
-        return li_fail("decay scan: unknown dtype %d", dtype);
-    }
-    if (e != cudaSuccess) return li_fail("decay_scan: launch failed: %s", cudaGetErrorString(e));
-    return li_check_launch("decay_scan");
+    LI_REQUIRE(S <= 65535 && heads <= 65535, "decay scan: %d sequences or %d heads in one launch", S, heads);
+#define LI_SCAN(RR)                                                                                                                          \
+    return dtype == LI_F32 ? launch_decay<float, RR>(qkv, stride, q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, S, heads, \
+                                                     d, dv, stream)                                                                          \
+                           : launch_decay<bf16, RR>(qkv, stride, q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, S, heads,  \
+                                                    d, dv, stream)
+    if (d <= 16) { LI_SCAN(2); }
+    if (d <= 32) { LI_SCAN(4); }
+    if (d <= 64) { LI_SCAN(8); }
+    if (d <= 128) { LI_SCAN(16); }
+    LI_SCAN(32);
+#undef LI_SCAN
 }
 
 LI_EXPORT int li_gated_rmsnorm(const float* y, const void* gate, int dtype, int gate_stride, int gate_off, const float* w, float eps, int mode,

@@ -297,7 +297,7 @@ def ssm_scan(xbc, proj, dt_col, dt_bias, A_log, D, state, q_start, slots, y32, h
         lo, hi = starts[s], starts[s + 1]
         if hi == lo:
             continue
-        S = state[sl[s], :heads * N * P].view(heads, N, P)
+        S = state[sl[s], :heads * N * P].view(heads, P, N).transpose(1, 2)          # kept column by column: [heads][P][N]
         for t in range(lo, hi):
             row = xbc[t].float()
             x = row[:inner].view(heads, P)
@@ -314,7 +314,7 @@ def decay_scan(qkv, q_col, k_col, v_col, decay, state, q_start, slots, out32, he
         lo, hi = starts[s], starts[s + 1]
         if hi == lo:
             continue
-        S = state[sl[s], :heads * dim * vdim].view(heads, dim, vdim)
+        S = state[sl[s], :heads * dim * vdim].view(heads, vdim, dim).transpose(1, 2)      # kept column by column: [heads][vdim][dim]
         for t in range(lo, hi):
             row = qkv[t].float()
             q = _silu(row[q_col:q_col + heads * dim]).view(heads, dim)
