@@ -18,7 +18,12 @@
 
 enum LiDtype : int { LI_F32 = 0, LI_BF16 = 1 };
 // What a matrix product does to its result: nothing, or the SwiGLU of interleaved gate and up columns.
-enum LiEpilogue : int { LI_EPILOGUE_NONE = 0, LI_EPILOGUE_SWIGLU = 1 };
+// LI_EPILOGUE_GLU_CLAMPED: the same columns, another activation (glu_of below); the product's `bias` argument then points
+// at its two parameters on the device, {limit, alpha}, since a gated product has no bias.
+enum LiEpilogue : int { LI_EPILOGUE_NONE = 0, LI_EPILOGUE_SWIGLU = 1, LI_EPILOGUE_GLU_CLAMPED = 2 };
+static inline bool li_epilogue_is_gated(int e) { return e == LI_EPILOGUE_SWIGLU || e == LI_EPILOGUE_GLU_CLAMPED; }
+// what a gated epilogue needs of the bias argument: none for SwiGLU, the parameters for the clamped unit
+static inline bool li_epilogue_bias_ok(int e, const float* bias) { return (e == LI_EPILOGUE_GLU_CLAMPED) == (bias != nullptr); }
 
 int li_fail(const char* fmt, ...);            // stores the message, returns 1
 int li_check_launch(const char* what);        // cudaGetLastError -> message
@@ -94,6 +99,17 @@ template <typename Tout>
 __device__ __forceinline__ float swiglu_of(float gate, float up) {
     if constexpr (sizeof(Tout) == 2) return up * __fdividef(gate, 1.0f + fast_exp2(-1.4426950408889634f * gate));
     else return up * (gate / (1.0f + expf(-gate)));
+}
+
+// The activation of a gated product's epilogue.  params null: SwiGLU.  Else {limit, alpha}: the gated unit with bounded
+// operands, g = min(gate, limit), u = clamp(up, -limit, limit), g / (1 + exp(-alpha g)) * (u + 1).
+template <typename Tout>
+__device__ __forceinline__ float glu_of(float gate, float up, const float* __restrict__ params) {
+    if (params == nullptr) return swiglu_of<Tout>(gate, up);
+    const float limit = __ldg(params), alpha = __ldg(params + 1);
+    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+    if constexpr (sizeof(Tout) == 2) return __fdividef(g, 1.0f + fast_exp2(-1.4426950408889634f * alpha * g)) * (u + 1.0f);
+    else return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
 }
 
 // Programmatic dependent launch.  A kernel launched through li_launch_pdl may begin while

@@ -618,8 +618,8 @@ int li_linear_tcgen05(const void* a, const void* w, const float* bias, void* out
     // wide products with a short k (gate|up): the persistent kernel, whose epilogue overlaps the next tile's products
     if (g_forced_tile == 6 || (g_forced_tile == 0 && g_forced_ksplit == 0 && li_tcgen05_persistent_wanted(M, N, K)))
         return li_linear_tcgen05_persistent(a, w, bias, out, dtype_out, M, N, K, epilogue, stream);
-    if (epilogue == LI_EPILOGUE_SWIGLU) {
-        LI_REQUIRE(N % 16 == 0 && bias == nullptr && dtype_out == LI_BF16,
+    if (li_epilogue_is_gated(epilogue)) {
+        LI_REQUIRE(N % 16 == 0 && li_epilogue_bias_ok(epilogue, bias) && dtype_out == LI_BF16,
                    "linear (tcgen05): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
         return launch<bf16, true>(a, w, bias, out, M, N, K, stream, g_forced_tile);
     }

@@ -198,8 +198,8 @@ bool li_tcgen05_persistent_wanted(int M, int N, int K) {
 
 int li_linear_tcgen05_persistent(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K, int epilogue,
                                  cudaStream_t stream) {
-    if (epilogue == LI_EPILOGUE_SWIGLU) {
-        LI_REQUIRE(N % 16 == 0 && bias == nullptr && dtype_out == LI_BF16,
+    if (li_epilogue_is_gated(epilogue)) {
+        LI_REQUIRE(N % 16 == 0 && li_epilogue_bias_ok(epilogue, bias) && dtype_out == LI_BF16,
                    "linear (tcgen05, persistent): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
         return launch<bf16, true>(a, w, bias, out, M, N, K, stream);
     }

@@ -349,8 +349,8 @@ int li_linear_gemv_bf16(const void* a, const void* w, const float* bias, void* o
                         int epilogue, cudaStream_t stream, const RowScale& rs) {
     LI_REQUIRE(li_gemv_bf16_accepts(M, N, K), "linear (gemv): refuses M=%d N=%d K=%d (M <= %d, K a multiple of 8)", M, N, K, kMaxM);
     LI_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0), "linear (gemv): operands must be 16-byte aligned");
-    if (epilogue == LI_EPILOGUE_SWIGLU) {
-        LI_REQUIRE(N % 16 == 0 && bias == nullptr && dtype_out == LI_BF16,
+    if (li_epilogue_is_gated(epilogue)) {
+        LI_REQUIRE(N % 16 == 0 && li_epilogue_bias_ok(epilogue, bias) && dtype_out == LI_BF16,
                    "linear (gemv): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
         return launch_nt<bf16, kEpiSwiglu>(a, w, bias, out, M, N, K, stream, rs);
     }

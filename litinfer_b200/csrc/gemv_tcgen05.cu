@@ -270,7 +270,7 @@ gemv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         const float up = __shfl_down_sync(0xffffffffu, v[j], 8);
                         if (j < M && (lane & 8) == 0 && row + 8 < N) {
                             const float gate = v[j];
-                            out[(size_t)j * half_n + col] = from_float<Tout>(swiglu_of<Tout>(gate, up));
+                            out[(size_t)j * half_n + col] = from_float<Tout>(glu_of<Tout>(gate, up, bias));
                         }
                     }
                 }
@@ -373,8 +373,8 @@ bool li_gemv_tcgen05_accepts(const void* a, const void* w, int M, int N, int K) 
 int li_linear_gemv_tcgen05(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K,
                            int epilogue, cudaStream_t stream, const RowScale& rs) {
     LI_REQUIRE(li_gemv_tcgen05_accepts(a, w, M, N, K), "linear (tcgen05 gemv): refuses M=%d N=%d K=%d (M <= 64, K a multiple of 8, 16-byte aligned operands)", M, N, K);
-    if (epilogue == LI_EPILOGUE_SWIGLU) {
-        LI_REQUIRE(N % 16 == 0 && bias == nullptr && dtype_out == LI_BF16,
+    if (li_epilogue_is_gated(epilogue)) {
+        LI_REQUIRE(N % 16 == 0 && li_epilogue_bias_ok(epilogue, bias) && dtype_out == LI_BF16,
                    "linear (tcgen05 gemv): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
         return launch_bt<bf16, kEpiSwiglu>(a, w, bias, out, M, N, K, stream, rs);
     }

@@ -46,7 +46,8 @@ __global__ void hc_read_norm_kernel(const float* __restrict__ xs, const float* _
 }
 
 template <typename T>
-__global__ void hc_update_kernel(float* __restrict__ xs, const T* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ out_w,
+__global__ void hc_update_kernel(float* __restrict__ xs, const T* __restrict__ y, const T* __restrict__ y2, float s1, float s2,
+                                 const float* __restrict__ mix, const float* __restrict__ out_w,
                                  const float* __restrict__ next_in, const float* __restrict__ next_w, float eps, T* __restrict__ next_out,
                                  int s, int H) {
     extern __shared__ float u_row[];
@@ -67,7 +68,8 @@ __global__ void hc_update_kernel(float* __restrict__ xs, const T* __restrict__ y
         float old[kMaxStreams];
 #pragma unroll
         for (int a = 0; a < kMaxStreams; ++a) old[a] = a < s ? x[(size_t)a * H + j] : 0.0f;
-        const float yj = to_float(y[(size_t)t * H + j]);
+        float yj = to_float(y[(size_t)t * H + j]);
+        if (y2) yj = fmaf(s1, yj, s2 * to_float(y2[(size_t)t * H + j]));        // the sublayer's output as a weighted sum of two
         float u = 0.0f;
 #pragma unroll
         for (int r = 0; r < kMaxStreams; ++r) {
@@ -136,9 +138,10 @@ LI_EXPORT int li_hc_read_norm(const float* xs, const float* in_w, const int* row
 }
 
 // xs[t, r] = sum_s mix[s, r] xs[t, s] + out_w[r] y[t]; then, unless next_out is null,
-// next_out[t] = RMSNorm(sum_r next_in[r] xs[t, r]) * next_w.
-LI_EXPORT int li_hc_update(float* xs, const void* y, int dtype, const float* mix, const float* out_w, const float* next_in, const float* next_w,
-                           float eps, void* next_out, int T, int s, int H, cudaStream_t stream) {
+// next_out[t] = RMSNorm(sum_r next_in[r] xs[t, r]) * next_w.  With y2, the sublayer's output is s1 y + s2 y2 (two mixers
+// side by side), summed in float.
+LI_EXPORT int li_hc_update(float* xs, const void* y, const void* y2, float s1, float s2, int dtype, const float* mix, const float* out_w,
+                           const float* next_in, const float* next_w, float eps, void* next_out, int T, int s, int H, cudaStream_t stream) {
     LI_REQUIRE(s >= 1 && s <= kMaxStreams, "hyper-connections: %d streams (1..%d)", s, kMaxStreams);
     LI_REQUIRE(H > 0 && (size_t)H * 4 <= 200 * 1024, "hyper-connections: width %d", H);
     LI_REQUIRE(next_out == nullptr || (next_in != nullptr && next_w != nullptr), "hc_update: the next read needs its weights");
@@ -147,11 +150,11 @@ LI_EXPORT int li_hc_update(float* xs, const void* y, int dtype, const float* mix
     cudaError_t e;
     if (dtype == LI_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(hc_update_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = li_launch_pdl(hc_update_kernel<float>, dim3(T), dim3(kThreads), smem, stream, xs, (const float*)y, mix, out_w, next_in, next_w, eps,
+        e = li_launch_pdl(hc_update_kernel<float>, dim3(T), dim3(kThreads), smem, stream, xs, (const float*)y, (const float*)y2, s1, s2, mix, out_w, next_in, next_w, eps,
                           (float*)next_out, s, H);
     } else if (dtype == LI_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(hc_update_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = li_launch_pdl(hc_update_kernel<bf16>, dim3(T), dim3(kThreads), smem, stream, xs, (const bf16*)y, mix, out_w, next_in, next_w, eps,
+        e = li_launch_pdl(hc_update_kernel<bf16>, dim3(T), dim3(kThreads), smem, stream, xs, (const bf16*)y, (const bf16*)y2, s1, s2, mix, out_w, next_in, next_w, eps,
                           (bf16*)next_out, s, H);
     } else {
         return li_fail("hyper-connections: unknown dtype %d", dtype);

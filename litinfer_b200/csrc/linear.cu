@@ -49,7 +49,7 @@ int few_rows_kernel(const void* a, const void* w, const void* out, int M, int N,
 int linear_impl(const void* a, const void* w, const float* bias, void* out, int dtype_in, int dtype_out, int M, int N, int K,
                 int epilogue, const RowScale& rs, cudaStream_t stream) {
     LI_REQUIRE(M >= 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
-    LI_REQUIRE(epilogue == LI_EPILOGUE_NONE || epilogue == LI_EPILOGUE_SWIGLU, "linear: unknown epilogue %d", epilogue);
+    LI_REQUIRE(epilogue == LI_EPILOGUE_NONE || li_epilogue_is_gated(epilogue), "linear: unknown epilogue %d", epilogue);
     if (M == 0) return 0;
     if (dtype_in == LI_BF16) {
         const int few = few_rows_kernel(a, w, out, M, N, K);
@@ -59,7 +59,7 @@ int linear_impl(const void* a, const void* w, const float* bias, void* out, int 
         if (li_tcgen05_accepts(a, w, out, dtype_out, M, N, K)) return li_linear_tcgen05(a, w, bias, out, dtype_out, M, N, K, epilogue, stream);
     }
     LI_REQUIRE(rs.ssq == nullptr, "linear: a factor per token exists in the kernels for at most 64 bfloat16 rows only (M=%d N=%d K=%d)", M, N, K);
-    LI_REQUIRE(epilogue == LI_EPILOGUE_NONE, "linear: the fused swiglu epilogue exists for bfloat16 with K a multiple of 8 only (M=%d N=%d K=%d)", M, N, K);
+    LI_REQUIRE(epilogue == LI_EPILOGUE_NONE, "linear: the fused gated epilogues exist for bfloat16 with K a multiple of 8 only (M=%d N=%d K=%d)", M, N, K);
     return li_linear_simt(a, w, bias, out, dtype_in, dtype_out, M, N, K, stream);
 }
 

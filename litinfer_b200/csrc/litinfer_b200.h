@@ -108,9 +108,9 @@ int li_hc_read_norm(const float* xs, const float* in_w, const int* rows, const f
     int T, int s, int H, cudaStream_t stream);
 
 /* xs[t, r] = sum_s mix[s, r] xs[t, s] + out_w[r] y[t] (all streams from the old ones); then, unless next_out is NULL,
- * next_out[t] = RMSNorm(sum_r next_in[r] xs[t, r]) * next_w. */
-int li_hc_update(float* xs, const void* y, int dtype, const float* mix, const float* out_w, const float* next_in, const float* next_w,
-    float eps, void* next_out, int T, int s, int H, cudaStream_t stream);
+ * next_out[t] = RMSNorm(sum_r next_in[r] xs[t, r]) * next_w.  y2 not NULL: the output is s1 y + s2 y2. */
+int li_hc_update(float* xs, const void* y, const void* y2, float s1, float s2, int dtype, const float* mix, const float* out_w,
+    const float* next_in, const float* next_w, float eps, void* next_out, int T, int s, int H, cudaStream_t stream);
 
 /* xs[t, a] = x[t] for every stream a. */
 int li_hc_expand(const float* x, float* xs, int T, int s, int H, cudaStream_t stream);
@@ -134,13 +134,20 @@ int li_conv_state_shift(const void* in, int dtype, int in_stride, int in_off, fl
  * [T, C] holds x | B | C; a sequence's tokens in order, its state read and written once (kept as [heads][P][N]). */
 int li_ssm_scan(const void* xbc, int dtype, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log,
     const float* D, float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads,
-    int P, int N, int groups, cudaStream_t stream);
+    int P, int N, int groups, const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream);
 
 /* Per head S [d, dv]: S = decay S + k v^T, out = S^T q, with q, k, v = silu of the columns at q_off, k_off, v_off
  * of qkv [T, stride]; the state is kept as [heads][dv][d]. */
 int li_decay_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const float* decay, float* state,
     long long state_stride, const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv,
-    cudaStream_t stream);
+    const int* seg, int mode, float* chunk_state, cudaStream_t stream);
+
+/* Long portions in chunks (seg: quadruples of begin, end, chunk, slot; S = their number): the scans run with mode 1 (every
+ * chunk from zeros, its end state to chunk_state, for li_ssm_scan its decay to chunk_decay), then li_scan_carry (runs:
+ * triples of first chunk, chunks, slot; a chunk's decay given, or token_decay[head] ^ length) turns chunk_state into the states the chunks start from and moves the slots on,
+ * then the scans with mode 2 (outputs).  Mode 0 without seg: every sequence in one piece. */
+int li_scan_carry(float* state, long long state_stride, float* chunk_state, const float* chunk_decay, const float* token_decay,
+    const int* seg, const int* runs, int nruns, int heads, int per_head, cudaStream_t stream);
 
 /* RMSNorm of y [T, n] (float) in `groups` equal parts, times w; mode 0: y is first multiplied by silu(gate), mode 1:
  * the result is multiplied by sigmoid(gate); gate [T, gate_stride] at column gate_off, in the run dtype like out. */

@@ -79,6 +79,15 @@ __global__ void conv_state_shift_kernel(const T* __restrict__ in, int in_stride,
 // vectors of kStage tokens that all its columns need (w, r, and the scalars) in shared memory once, with the
 // activations applied, and the columns then run through them with three shuffles a token for the sum.  The state is
 // stored column by column ([head][column][element]) so that it is read and written in whole lines.
+//
+// Long portions are cut into chunks that run side by side (a sequence alone has too few columns to fill the GPU, and a
+// walk over thousands of tokens is bound by its latency): `seg` names the chunks (begin, end, chunk, slot) and `mode` says
+// which of three passes this is.  kScanLocal: every chunk from a state of zeros, no outputs, its end state to
+// chunk_state[chunk].  li_scan_carry then walks each sequence's chunks in order, S <- decay(chunk) S + end state, and
+// leaves in chunk_state[chunk] the state the chunk starts from (and the sequence's last state in its slot).  kScanApply:
+// every chunk again from that state, with outputs.  Without `seg` (kScanWhole) a sequence is one piece, read from and
+// written to its slot: steps of single tokens and short portions.
+enum { kScanWhole = 0, kScanLocal = 1, kScanApply = 2 };
 constexpr int kStage = 16;          // tokens staged at a time
 constexpr int kColWarps = 4;        // warps a block
 constexpr int kCols = kColWarps * 4;
@@ -94,7 +103,8 @@ template <typename T, int R>
 __global__ void __launch_bounds__(kColWarps * 32)
 ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, int dt_stride, const float* __restrict__ dt_bias,
                 const float* __restrict__ A_log, const float* __restrict__ D, float* __restrict__ state, long long state_stride,
-                const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ y, int heads, int P, int N, int groups) {
+                const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ y, int heads, int P, int N, int groups,
+                const int* __restrict__ seg, int mode, float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
     extern __shared__ float smem[];
     float* Bs = smem;                           // [kStage][N]
     float* Cs = Bs + (size_t)kStage * N;        // [kStage][N]
@@ -103,8 +113,14 @@ ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, 
     float* das = dts + kStage;                  // [kStage] decay
     pdl_launch_dependents();
     pdl_wait();
-    const int h = blockIdx.y, s = blockIdx.z;
-    const int q0 = q_start[s], q1 = q_start[s + 1];
+    const int h = blockIdx.y;
+    int q0, q1, slot, chunk = 0;
+    if (seg) {
+        const int4 sg = reinterpret_cast<const int4*>(seg)[blockIdx.z];
+        q0 = sg.x; q1 = sg.y; chunk = sg.z; slot = sg.w;
+    } else {
+        q0 = q_start[blockIdx.z]; q1 = q_start[blockIdx.z + 1]; slot = slots[blockIdx.z];
+    }
     if (q1 <= q0) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int m = lane & 7;
@@ -113,19 +129,30 @@ ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, 
     const bool live = c < P;
     const int g = h / (heads / groups);
     const int inner = heads * P;
-    float* st = state + (size_t)slots[s] * state_stride + ((size_t)h * P + (live ? c : 0)) * N;
+    const size_t col_at = ((size_t)h * P + (live ? c : 0)) * N;
+    float* st = state + (size_t)slot * state_stride + col_at;
+    float* cst = chunk_state ? chunk_state + (size_t)chunk * heads * P * N + col_at : nullptr;
+    const float* from = mode == kScanWhole ? st : cst;
     float S[R];
 #pragma unroll
-    for (int k = 0; k < R; ++k) S[k] = (live && m + 8 * k < N) ? st[m + 8 * k] : 0.0f;
+    for (int k = 0; k < R; ++k) S[k] = (mode != kScanLocal && live && m + 8 * k < N) ? from[m + 8 * k] : 0.0f;
     const float rate = expf(A_log[h]), bias = dt_bias[h], skip = D[h];
+    if (mode == kScanLocal && blockIdx.x == 0 && warp == 0) {
+        // the chunk's decay as a whole, for the pass that carries states from chunk to chunk
+        float sum = 0.0f;
+        for (int t = q0 + lane; t < q1; t += 32) sum += -rate * softplus_f(to_float(dt_raw[(size_t)t * dt_stride + h]) + bias);
+        sum = warp_sum(sum);
+        if (lane == 0) chunk_decay[(size_t)chunk * heads + h] = expf(sum);
+    }
     for (int t0 = q0; t0 < q1; t0 += kStage) {
         const int nt = min(kStage, q1 - t0);
         __syncthreads();                                   // the stage before has been used up
-        for (int e = threadIdx.x; e < nt * N; e += blockDim.x) {
-            const int tk = e / N, n = e - tk * N;
+        for (int tk = warp; tk < nt; tk += kColWarps) {
             const T* row = xbc + (size_t)(t0 + tk) * C;
-            Bs[tk * N + n] = to_float(row[inner + g * N + n]);
-            Cs[tk * N + n] = to_float(row[inner + (groups + g) * N + n]);
+            for (int n = lane; n < N; n += 32) {
+                Bs[tk * N + n] = to_float(row[inner + g * N + n]);
+                Cs[tk * N + n] = to_float(row[inner + (groups + g) * N + n]);
+            }
         }
         for (int e = threadIdx.x; e < nt * kCols; e += blockDim.x) {
             const int tk = e / kCols, j = e - tk * kCols;
@@ -153,13 +180,14 @@ ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, 
                 }
             }
             acc = oct_sum(acc);
-            if (live && m == 0) y[(size_t)(t0 + tk) * inner + h * P + c] = fmaf(skip, x, acc);
+            if (mode != kScanLocal && live && m == 0) y[(size_t)(t0 + tk) * inner + h * P + c] = fmaf(skip, x, acc);
         }
     }
-    if (live) {
+    if (live && mode != kScanApply) {
+        float* to = mode == kScanWhole ? st : cst;
 #pragma unroll
         for (int k = 0; k < R; ++k)
-            if (m + 8 * k < N) st[m + 8 * k] = S[k];
+            if (m + 8 * k < N) to[m + 8 * k] = S[k];
     }
 }
 
@@ -168,34 +196,44 @@ template <typename T, int R>
 __global__ void __launch_bounds__(kColWarps * 32)
 decay_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots,
-                  float* __restrict__ out, int heads, int d, int dv) {
+                  float* __restrict__ out, int heads, int d, int dv, const int* __restrict__ seg, int mode, float* __restrict__ chunk_state) {
     extern __shared__ float smem[];
     float* qs = smem;                           // [kStage][d]
     float* ks = qs + (size_t)kStage * d;        // [kStage][d]
     float* vs = ks + (size_t)kStage * d;        // [kStage][kCols]
     pdl_launch_dependents();
     pdl_wait();
-    const int h = blockIdx.y, s = blockIdx.z;
-    const int q0 = q_start[s], q1 = q_start[s + 1];
+    const int h = blockIdx.y;
+    int q0, q1, slot, chunk = 0;
+    if (seg) {
+        const int4 sg = reinterpret_cast<const int4*>(seg)[blockIdx.z];
+        q0 = sg.x; q1 = sg.y; chunk = sg.z; slot = sg.w;
+    } else {
+        q0 = q_start[blockIdx.z]; q1 = q_start[blockIdx.z + 1]; slot = slots[blockIdx.z];
+    }
     if (q1 <= q0) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int m = lane & 7;
     const int col0 = blockIdx.x * kCols;
     const int c = col0 + warp * 4 + (lane >> 3);
     const bool live = c < dv;
-    float* st = state + (size_t)slots[s] * state_stride + ((size_t)h * dv + (live ? c : 0)) * d;
+    const size_t col_at = ((size_t)h * dv + (live ? c : 0)) * d;
+    float* st = state + (size_t)slot * state_stride + col_at;
+    float* cst = chunk_state ? chunk_state + (size_t)chunk * heads * dv * d + col_at : nullptr;
+    const float* from = mode == kScanWhole ? st : cst;
     float S[R];
 #pragma unroll
-    for (int k = 0; k < R; ++k) S[k] = (live && m + 8 * k < d) ? st[m + 8 * k] : 0.0f;
+    for (int k = 0; k < R; ++k) S[k] = (mode != kScanLocal && live && m + 8 * k < d) ? from[m + 8 * k] : 0.0f;
     const float lam = decay[h];
     for (int t0 = q0; t0 < q1; t0 += kStage) {
         const int nt = min(kStage, q1 - t0);
         __syncthreads();
-        for (int e = threadIdx.x; e < nt * d; e += blockDim.x) {
-            const int tk = e / d, i = e - tk * d;
+        for (int tk = warp; tk < nt; tk += kColWarps) {
             const T* row = qkv + (size_t)(t0 + tk) * stride;
-            qs[tk * d + i] = silu_f(to_float(row[q_off + h * d + i]));
-            ks[tk * d + i] = silu_f(to_float(row[k_off + h * d + i]));
+            for (int i = lane; i < d; i += 32) {
+                if (mode != kScanLocal) qs[tk * d + i] = silu_f(to_float(row[q_off + h * d + i]));
+                ks[tk * d + i] = silu_f(to_float(row[k_off + h * d + i]));
+            }
         }
         for (int e = threadIdx.x; e < nt * kCols; e += blockDim.x) {
             const int tk = e / kCols, j = e - tk * kCols;
@@ -216,15 +254,44 @@ decay_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, i
                     acc = fmaf(S[k], qq[i], acc);
                 }
             }
-            acc = oct_sum(acc);
-            if (live && m == 0) out[(size_t)(t0 + tk) * heads * dv + h * dv + c] = acc;
+            if (mode != kScanLocal) {
+                acc = oct_sum(acc);
+                if (live && m == 0) out[(size_t)(t0 + tk) * heads * dv + h * dv + c] = acc;
+            }
         }
     }
-    if (live) {
+    if (live && mode != kScanApply) {
+        float* to = mode == kScanWhole ? st : cst;
 #pragma unroll
         for (int k = 0; k < R; ++k)
-            if (m + 8 * k < d) st[m + 8 * k] = S[k];
+            if (m + 8 * k < d) to[m + 8 * k] = S[k];
     }
+}
+
+// Between the two passes over chunks: for each run of chunks (a sequence's, in order) S starts as the slot's state;
+// chunk_state[chunk] (the chunk's end state from zeros) is replaced by the state the chunk starts from, and
+// S <- decay[chunk, head] S + end state.  The last S goes back to the slot.
+__global__ void scan_carry_kernel(float* __restrict__ state, long long state_stride, float* __restrict__ chunk_state,
+                                  const float* __restrict__ chunk_decay, const float* __restrict__ token_decay, const int* __restrict__ seg,
+                                  const int* __restrict__ runs, int heads, int per_head) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int first = runs[3 * blockIdx.y], count = runs[3 * blockIdx.y + 1], slot = runs[3 * blockIdx.y + 2];
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    const int elements = heads * per_head;
+    if (e >= elements) return;
+    const int h = e / per_head;
+    float* st = state + (size_t)slot * state_stride + e;
+    float S = *st;
+    for (int c = first; c < first + count; ++c) {
+        float* z = chunk_state + (size_t)c * elements + e;
+        const float end_state = *z;
+        *z = S;
+        // the chunk's decay: given, or a constant per token and head to the power of the chunk's length
+        const float dec = chunk_decay ? chunk_decay[(size_t)c * heads + h] : powf(token_decay[h], (float)(seg[4 * c + 1] - seg[4 * c]));
+        S = fmaf(dec, S, end_state);
+    }
+    *st = S;
 }
 
 // One block per (token, group).  mode 0: v = y silu(z), out = v rinv w; mode 1: out = y rinv w sigmoid(z).
@@ -301,11 +368,12 @@ LI_EXPORT int li_conv_state_shift(const void* in, int dtype, int in_stride, int 
 template <typename T, int R>
 static int launch_ssm(const void* xbc, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log, const float* D,
                       float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads, int P, int N,
-                      int groups, cudaStream_t stream) {
+                      int groups, const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream) {
     const size_t smem = ((size_t)2 * kStage * N + kStage * kCols + 2 * kStage) * sizeof(float);
     if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaError_t e = li_launch_pdl(ssm_scan_kernel<T, R>, dim3(ceil_div(P, kCols), heads, S), dim3(kColWarps * 32), smem, stream, (const T*)xbc, C,
-                                  (const T*)dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, heads, P, N, groups);
+                                  (const T*)dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, heads, P, N, groups, seg, mode,
+                                  chunk_state, chunk_decay);
     if (e != cudaSuccess) return li_fail("ssm_scan: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("ssm_scan");
 }
@@ -313,7 +381,9 @@ static int launch_ssm(const void* xbc, int C, const void* dt_raw, int dt_stride,
 // The state of a slot: [heads][P][N] (a column of the head's N x P matrix at a time).
 LI_EXPORT int li_ssm_scan(const void* xbc, int dtype, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log,
                           const float* D, float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads,
-                          int P, int N, int groups, cudaStream_t stream) {
+                          int P, int N, int groups, const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream) {
+    LI_REQUIRE(mode == kScanWhole ? seg == nullptr : (seg != nullptr && chunk_state != nullptr && chunk_decay != nullptr && (uintptr_t)seg % 16 == 0),
+               "state-space scan: pass %d needs the chunks, their states and their decays (or none of them)", mode);
     LI_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0, "state-space scan: %d heads in %d groups", heads, groups);
     LI_REQUIRE(P > 0 && N > 0 && N <= 256, "state-space scan: head size %d, state size %d (at most 256)", P, N);
     LI_REQUIRE(C == heads * P + 2 * groups * N, "state-space scan: %d channels for %d heads of %d and %d groups of %d", C, heads, P, groups, N);
@@ -322,9 +392,9 @@ LI_EXPORT int li_ssm_scan(const void* xbc, int dtype, int C, const void* dt_raw,
     LI_REQUIRE(S <= 65535 && heads <= 65535, "state-space scan: %d sequences or %d heads in one launch", S, heads);
 #define LI_SCAN(RR)                                                                                                                            \
     return dtype == LI_F32 ? launch_ssm<float, RR>(xbc, C, dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, S, heads, \
-                                                   P, N, groups, stream)                                                                       \
+                                                   P, N, groups, seg, mode, chunk_state, chunk_decay, stream)                                  \
                            : launch_ssm<bf16, RR>(xbc, C, dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, S, heads,  \
-                                                  P, N, groups, stream)
+                                                  P, N, groups, seg, mode, chunk_state, chunk_decay, stream)
     if (N <= 16) { LI_SCAN(2); }
     if (N <= 32) { LI_SCAN(4); }
     if (N <= 64) { LI_SCAN(8); }
@@ -335,11 +405,12 @@ LI_EXPORT int li_ssm_scan(const void* xbc, int dtype, int C, const void* dt_raw,
 
 template <typename T, int R>
 static int launch_decay(const void* qkv, int stride, int q_off, int k_off, int v_off, const float* decay, float* state, long long state_stride,
-                        const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv, cudaStream_t stream) {
+                        const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv, const int* seg, int mode,
+                        float* chunk_state, cudaStream_t stream) {
     const size_t smem = ((size_t)2 * kStage * d + kStage * kCols) * sizeof(float);
     if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaError_t e = li_launch_pdl(decay_scan_kernel<T, R>, dim3(ceil_div(dv, kCols), heads, S), dim3(kColWarps * 32), smem, stream, (const T*)qkv, stride,
-                                  q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, heads, d, dv);
+                                  q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, heads, d, dv, seg, mode, chunk_state);
     if (e != cudaSuccess) return li_fail("decay_scan: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("decay_scan");
 }
@@ -347,22 +418,38 @@ static int launch_decay(const void* qkv, int stride, int q_off, int k_off, int v
 // The state of a slot: [heads][dv][d] (a column of the head's d x dv matrix at a time).
 LI_EXPORT int li_decay_scan(const void* qkv, int dtype, int stride, int q_off, int k_off, int v_off, const float* decay, float* state,
                             long long state_stride, const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv,
-                            cudaStream_t stream) {
+                            const int* seg, int mode, float* chunk_state, cudaStream_t stream) {
+    LI_REQUIRE(mode == kScanWhole ? seg == nullptr : (seg != nullptr && chunk_state != nullptr && (uintptr_t)seg % 16 == 0),
+               "decay scan: pass %d needs the chunks and their states (or none of them)", mode);
     LI_REQUIRE(heads > 0 && d > 0 && d <= 256 && dv > 0, "decay scan: %d heads of %d x %d (keys of at most 256)", heads, d, dv);
     LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "decay scan: unknown dtype %d", dtype);
     if (S == 0) return 0;
     LI_REQUIRE(S <= 65535 && heads <= 65535, "decay scan: %d sequences or %d heads in one launch", S, heads);
 #define LI_SCAN(RR)                                                                                                                          \
     return dtype == LI_F32 ? launch_decay<float, RR>(qkv, stride, q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, S, heads, \
-                                                     d, dv, stream)                                                                          \
+                                                     d, dv, seg, mode, chunk_state, stream)                                                  \
                            : launch_decay<bf16, RR>(qkv, stride, q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, S, heads,  \
-                                                    d, dv, stream)
+                                                    d, dv, seg, mode, chunk_state, stream)
     if (d <= 16) { LI_SCAN(2); }
     if (d <= 32) { LI_SCAN(4); }
     if (d <= 64) { LI_SCAN(8); }
     if (d <= 128) { LI_SCAN(16); }
     LI_SCAN(32);
 #undef LI_SCAN
+}
+
+// See scan_carry_kernel.  runs: triples (first chunk, chunks, slot); per_head: state elements of one head.  The decay of a
+// chunk and head: chunk_decay[chunk, head], or (chunk_decay null) token_decay[head] to the power of the chunk's length.
+LI_EXPORT int li_scan_carry(float* state, long long state_stride, float* chunk_state, const float* chunk_decay, const float* token_decay,
+                            const int* seg, const int* runs, int nruns, int heads, int per_head, cudaStream_t stream) {
+    LI_REQUIRE(heads > 0 && per_head > 0, "scan carry: %d heads of %d elements", heads, per_head);
+    LI_REQUIRE(chunk_decay != nullptr || (token_decay != nullptr && seg != nullptr), "scan carry: no decay given");
+    if (nruns == 0) return 0;
+    LI_REQUIRE(nruns <= 65535, "scan carry: %d sequences in one launch", nruns);
+    cudaError_t e = li_launch_pdl(scan_carry_kernel, dim3(ceil_div(heads * per_head, 256), nruns), dim3(256), 0, stream, state, state_stride, chunk_state,
+                                  chunk_decay, token_decay, seg, runs, heads, per_head);
+    if (e != cudaSuccess) return li_fail("scan_carry: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("scan_carry");
 }
 
 LI_EXPORT int li_gated_rmsnorm(const float* y, const void* gate, int dtype, int gate_stride, int gate_off, const float* w, float eps, int mode,

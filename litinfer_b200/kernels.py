@@ -205,7 +205,8 @@ def logit_cap(logits: torch.Tensor, cap: float) -> None:
     _check(library().li_logit_cap(_p(logits), _l(logits.numel()), _f(cap), _stream(logits)), "logit_cap")
 
 
-EPILOGUES = {None: 0, "swiglu": 1}
+EPILOGUES = {None: 0, "swiglu": 1, "glu_clamped": 2}
+GATED = ("swiglu", "glu_clamped")
 
 
 def _linear_args(a, weight, bias, out, epilogue):
@@ -217,14 +218,27 @@ def _linear_args(a, weight, bias, out, epilogue):
         _need(bias, "linear bias", torch.float32, (N,))
     if epilogue not in EPILOGUES:
         raise KernelError(f"linear: unknown epilogue {epilogue!r}")
-    _need(out, "linear output", None, (M, N // 2 if epilogue == "swiglu" else N))
+    _need(out, "linear output", None, (M, N // 2 if epilogue in GATED else N))
     if out.dtype not in (a.dtype, torch.float32):
         raise KernelError(f"linear output must be {a.dtype} or float32, got {out.dtype}")
     return M, N, Kd
 
 
+def _gated_params(epilogue, bias, epilogue_params):
+    """What goes in the bias argument of the library's call: a gated product has no bias, and the clamped unit's two
+    parameters (float32 ``[limit, alpha]`` on the device) travel in its place."""
+    if epilogue == "glu_clamped":
+        if bias is not None or epilogue_params is None:
+            raise KernelError("linear: the glu_clamped epilogue takes no bias and needs epilogue_params = [limit, alpha]")
+        _need(epilogue_params, "epilogue parameters", torch.float32, (2,))
+        return epilogue_params
+    if epilogue_params is not None:
+        raise KernelError(f"linear: epilogue {epilogue!r} takes no parameters")
+    return bias
+
+
 def linear(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-           epilogue: Optional[str] = None, row_scale=None) -> None:
+           epilogue: Optional[str] = None, row_scale=None, epilogue_params: Optional[torch.Tensor] = None) -> None:
     """out[M, N] = a[M, K] weight[N, K]^T (+ bias[N]); float32 accumulation;
     out is in the run dtype or float32.
 
@@ -233,8 +247,11 @@ def linear(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
     unless :func:`linear_scaled_accepts`.
 
     ``epilogue="swiglu"`` (bfloat16 only): ``weight`` holds gate and up rows interleaved in
-    groups of 8 (see :func:`interleave_gate_up`) and out[M, N / 2] = up * gate / (1 + exp(-gate))."""
+    groups of 8 (see :func:`interleave_gate_up`) and out[M, N / 2] = up * gate / (1 + exp(-gate)).
+    ``epilogue="glu_clamped"`` with ``epilogue_params`` = float32 ``[limit, alpha]`` on the device: the same layout, and
+    out = g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
     M, N, Kd = _linear_args(a, weight, bias, out, epilogue)
+    bias = _gated_params(epilogue, bias, epilogue_params)
     if M == 0:
         return
     if row_scale is not None:
@@ -311,10 +328,11 @@ LINEAR_IMPLEMENTATIONS = {"simt": 0, "gemv": 1, "tcgen05": 2, "gemv_tcgen05": 3}
 
 
 def linear_with(which: str, a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                epilogue: Optional[str] = None) -> None:
+                epilogue: Optional[str] = None, epilogue_params: Optional[torch.Tensor] = None) -> None:
     """:func:`linear` through one named kernel (``simt``, ``gemv``, ``tcgen05``, ``gemv_tcgen05``); an error
     if that kernel refuses the sizes.  For tests and measurements of a kernel alone."""
     M, N, Kd = _linear_args(a, weight, bias, out, epilogue)
+    bias = _gated_params(epilogue, bias, epilogue_params)
     _check(library().li_linear_with(_i(LINEAR_IMPLEMENTATIONS[which]), _p(a), _p(weight), _p(bias), _p(out), _i(_dt(a)),
                                     _i(_dt(out)), _i(M), _i(N), _i(Kd), _i(EPILOGUES[epilogue]), _stream(out)), f"linear[{which}]")
 
@@ -476,6 +494,19 @@ def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: f
     _check(library().li_glu_clamped(_p(gate_up), _p(out), _i(_dt(out)), _i(T), _i(I2 // 2), _f(limit), _f(alpha), _stream(out)), "glu_clamped")
 
 
+class WeightedPair:
+    """Two activations that stand for ``sa * a + sb * b`` (two mixers side by side) until a kernel that consumes the sum
+    takes it in (:func:`hc_update`); :meth:`materialize` adds them up with a kernel of its own."""
+
+    def __init__(self, a: torch.Tensor, b: torch.Tensor, sa: float, sb: float) -> None:
+        self.a, self.b, self.sa, self.sb = a, b, float(sa), float(sb)
+
+    def materialize(self) -> torch.Tensor:
+        out = torch.empty_like(self.a)
+        weighted_sum2(self.a, self.b, self.sa, self.sb, out)
+        return out
+
+
 def weighted_sum2(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float, out: torch.Tensor) -> None:
     """out = sa * a + sb * b (run dtype in and out, the sum in float32)."""
     _need(a, "first operand")
@@ -523,11 +554,16 @@ def hc_read_norm(xs: torch.Tensor, in_w: Optional[torch.Tensor], rows: Optional[
                                      _stream(out)), "hc_read_norm")
 
 
-def hc_update(xs: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_w: torch.Tensor, next_in: Optional[torch.Tensor] = None,
+def hc_update(xs: torch.Tensor, y, mix: torch.Tensor, out_w: torch.Tensor, next_in: Optional[torch.Tensor] = None,
               next_weight: Optional[torch.Tensor] = None, eps: float = 0.0, next_out: Optional[torch.Tensor] = None) -> None:
     """xs[t, r] = sum_s mix[s, r] xs[t, s] + out_w[r] y[t], every stream from the old ones, in place; with ``next_out``
-    also the next sublayer's input: next_out[t] = rmsnorm(sum_r next_in[r] xs[t, r]) * next_weight."""
+    also the next sublayer's input: next_out[t] = rmsnorm(sum_r next_in[r] xs[t, r]) * next_weight.
+    ``y`` may be a :class:`WeightedPair` (a, b, sa, sb): the sublayer's output is then sa * a + sb * b, summed in float32."""
     T, s, H = xs.shape
+    y2, s1, s2 = None, 1.0, 0.0
+    if isinstance(y, WeightedPair):
+        y, y2, s1, s2 = y.a, y.b, float(y.sa), float(y.sb)
+        _need(y2, "sublayer output (second)", y.dtype, (T, H))
     _need(xs, "streams", torch.float32)
     _need(y, "sublayer output", None, (T, H))
     _need(mix, "stream mix", torch.float32, (s, s))
@@ -536,7 +572,7 @@ def hc_update(xs: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_w: torch
         _need(next_in, "read weights", torch.float32, (s,))
         _need(next_weight, "rmsnorm weight", torch.float32, (H,))
         _need(next_out, "normalised output", y.dtype, (T, H))
-    _check(library().li_hc_update(_p(xs), _p(y), _i(_dt(y)), _p(mix), _p(out_w), _p(next_in if next_out is not None else None),
+    _check(library().li_hc_update(_p(xs), _p(y), _p(y2), _f(s1), _f(s2), _i(_dt(y)), _p(mix), _p(out_w), _p(next_in if next_out is not None else None),
                                   _p(next_weight if next_out is not None else None), _f(eps), _p(next_out), _i(T), _i(s), _i(H), _stream(xs)),
            "hc_update")
 
@@ -586,12 +622,48 @@ def conv_state_shift(x: torch.Tensor, col: int, channels: int, taps: int, state:
                                          _i(channels), _i(taps), _stream(x)), "conv_state_shift")
 
 
+class ScanChunks:
+    """The long portions of a step cut into chunks that the scans run side by side (see :func:`ssm_scan`):
+    ``seg`` int32 ``[chunks, 4]`` (first token, end, chunk, state slot) and ``runs`` int32 ``[sequences, 3]`` (first chunk,
+    chunks, state slot) on the device.  Made from the step's host-side metadata, once per step."""
+
+    LENGTH = 64              # tokens a chunk
+    FROM = 128               # the longest portion of a step from which its scans run in chunks
+
+    def __init__(self, q_start, slots, device, length: int = LENGTH) -> None:
+        seg, runs = [], []
+        for s, slot in enumerate(slots):
+            lo, hi = int(q_start[s]), int(q_start[s + 1])
+            if hi <= lo:
+                continue
+            first = len(seg)
+            for b in range(lo, hi, length):
+                seg.append((b, min(hi, b + length), len(seg), int(slot)))
+            runs.append((first, len(seg) - first, int(slot)))
+        self.count, self.nruns = len(seg), len(runs)
+        self.seg = torch.tensor(seg, dtype=torch.int32).to(device)
+        self.runs = torch.tensor(runs, dtype=torch.int32).to(device)
+
+
+def _scan_passes(chunks: Optional["ScanChunks"], elements: int, heads: int, device):
+    """(seg pointer, S, mode, chunk states, chunk decays) of every pass a scan makes: one over whole sequences, or two over chunks."""
+    if chunks is None:
+        return None
+    return (torch.empty((chunks.count, elements), dtype=torch.float32, device=device),
+            torch.empty((chunks.count, heads), dtype=torch.float32, device=device))
+
+
 def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor,
              state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, y32: torch.Tensor, heads: int, head_dim: int,
-             state_size: int, groups: int) -> None:
+             state_size: int, groups: int, chunks: Optional[ScanChunks] = None) -> None:
     """The selective state-space recurrence per head, state ``S [state_size, head_dim]`` at the start of ``state[slot]``:
     ``dt = softplus(proj[t, dt_col + h] + dt_bias[h])``; ``S = exp(-exp(A_log[h]) dt) S + dt B_t x_t^T``;
-    ``y_t = S^T C_t + D[h] x_t``.  ``xbc`` [T, heads * head_dim + 2 * groups * state_size] holds x | B | C."""
+    ``y_t = S^T C_t + D[h] x_t``.  ``xbc`` [T, heads * head_dim + 2 * groups * state_size] holds x | B | C.  The state
+    is kept column by column, ``[heads, head_dim, state_size]``.
+
+    ``chunks``: the step's sequences cut into chunks (a step with long portions).  Every chunk then runs twice, side by side
+    with the others: from a state of zeros to find what it adds, and, after the states have been carried from chunk to
+    chunk in order (:func:`ScanChunks`, ``li_scan_carry``), from the state it really starts with, for its outputs."""
     T, C = xbc.shape
     _need(xbc, "x|B|C")
     _need(proj, "projection", xbc.dtype)
@@ -604,16 +676,27 @@ def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.
     if heads * head_dim * state_size > state.shape[1] or dt_col + heads > proj.shape[1]:
         raise KernelError("ssm_scan: the state or the projection is too small")
     dt_ptr = ctypes.c_void_p(proj.data_ptr() + dt_col * proj.element_size())
-    _check(library().li_ssm_scan(_p(xbc), _i(_dt(xbc)), _i(C), dt_ptr, _i(proj.shape[1]), _p(dt_bias), _p(A_log), _p(D), st, stride,
-                                 _p(q_start), _p(slots), _p(y32), _i(S), _i(heads), _i(head_dim), _i(state_size), _i(groups), _stream(y32)),
-           "ssm_scan")
+
+    def run(seg, n, mode, cstate, cdecay):
+        _check(library().li_ssm_scan(_p(xbc), _i(_dt(xbc)), _i(C), dt_ptr, _i(proj.shape[1]), _p(dt_bias), _p(A_log), _p(D), st, stride,
+                                     _p(q_start), _p(slots), _p(y32), _i(n), _i(heads), _i(head_dim), _i(state_size), _i(groups),
+                                     _p(seg), _i(mode), _p(cstate), _p(cdecay), _stream(y32)), "ssm_scan")
+
+    if chunks is None or chunks.count == 0:
+        return run(None, S, 0, None, None)
+    cstate, cdecay = _scan_passes(chunks, heads * head_dim * state_size, heads, xbc.device)
+    run(chunks.seg, chunks.count, 1, cstate, cdecay)
+    _check(library().li_scan_carry(st, stride, _p(cstate), _p(cdecay), _p(None), _p(chunks.seg), _p(chunks.runs), _i(chunks.nruns), _i(heads),
+                                   _i(head_dim * state_size), _stream(y32)), "scan_carry")
+    run(chunks.seg, chunks.count, 2, cstate, cdecay)
 
 
 def decay_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
-               slots: torch.Tensor, out32: torch.Tensor, heads: int, dim: int, vdim: int) -> None:
+               slots: torch.Tensor, out32: torch.Tensor, heads: int, dim: int, vdim: int, chunks: Optional[ScanChunks] = None) -> None:
     """Linear attention with a constant decay per head, state ``S [dim, vdim]`` per head at the start of
     ``state[slot]``: ``S = decay[h] S + k_t v_t^T``; ``out_t = S^T q_t``; q, k, v are silu of the columns of ``qkv``
-    at ``q_col``, ``k_col``, ``v_col`` (heads side by side)."""
+    at ``q_col``, ``k_col``, ``v_col`` (heads side by side).  The state is kept column by column, ``[heads, vdim, dim]``.
+    ``chunks``: as in :func:`ssm_scan`."""
     T = qkv.shape[0]
     _need(qkv, "q|k|v")
     _need(decay, "decay", torch.float32, (heads,))
@@ -623,8 +706,19 @@ def decay_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: tor
     st, stride, _ = _state_args(state, 0)
     if heads * dim * vdim > state.shape[1]:
         raise KernelError("decay_scan: the state is too small")
-    _check(library().li_decay_scan(_p(qkv), _i(_dt(qkv)), _i(qkv.shape[1]), _i(q_col), _i(k_col), _i(v_col), _p(decay), st, stride, _p(q_start),
-                                   _p(slots), _p(out32), _i(S), _i(heads), _i(dim), _i(vdim), _stream(out32)), "decay_scan")
+
+    def run(seg, n, mode, cstate):
+        _check(library().li_decay_scan(_p(qkv), _i(_dt(qkv)), _i(qkv.shape[1]), _i(q_col), _i(k_col), _i(v_col), _p(decay), st, stride, _p(q_start),
+                                       _p(slots), _p(out32), _i(n), _i(heads), _i(dim), _i(vdim), _p(seg), _i(mode), _p(cstate), _stream(out32)),
+               "decay_scan")
+
+    if chunks is None or chunks.count == 0:
+        return run(None, S, 0, None)
+    cstate = torch.empty((chunks.count, heads * dim * vdim), dtype=torch.float32, device=qkv.device)
+    run(chunks.seg, chunks.count, 1, cstate)
+    _check(library().li_scan_carry(st, stride, _p(cstate), _p(None), _p(decay), _p(chunks.seg), _p(chunks.runs), _i(chunks.nruns), _i(heads),
+                                   _i(dim * vdim), _stream(out32)), "scan_carry")
+    run(chunks.seg, chunks.count, 2, cstate)
 
 
 def gated_rmsnorm(y32: torch.Tensor, gate: torch.Tensor, gate_col: int, weight: torch.Tensor, eps: float, groups: int, gate_first: bool,

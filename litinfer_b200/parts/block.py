@@ -152,7 +152,8 @@ class HyperPreNormBlock(Block):
             raise ValueError("a block over several streams cannot take an output that is still to be added")
         h = carry.normed if carry is not None and carry.normed is not None else self.mixer_norm.streams_forward(xs, self.mixer_connection.read)
         nxt = next_entry if isinstance(next_entry, StreamsEntry) else None
-        y = self.mixer.forward(h, ctx, cache)
+        # (a mixer of two side by side hands both outputs over: the write-back adds them up)
+        y = self.mixer.forward_pair(h, ctx, cache) if getattr(self.mixer, "produces_pairs", False) else self.mixer.forward(h, ctx, cache)
         if self.feed_forward is None:
             h = self._write_back(xs, y, self.mixer_connection, nxt.norm if nxt else None, nxt.read if nxt else None)
             return xs, (Carry(normed=h) if h is not None else None)

@@ -79,12 +79,17 @@ class FusedLinear:
 class GateUpLinear(FusedLinear):
     """gate and up maps of a gated feed-forward.  In bfloat16, with sizes that are multiples of
     8, the two matrices are interleaved in groups of 8 rows when bound and the product's
-    epilogue applies up * silu(gate), so the [tokens, 2 * intermediate] product never goes to
-    memory.  Otherwise (the 32-bit path) the fused product is followed by the swiglu kernel."""
+    epilogue applies the gated activation (up * silu(gate), or the unit with bounded operands), so the
+    [tokens, 2 * intermediate] product never goes to memory.  Otherwise (the 32-bit path) the fused product is followed by the swiglu kernel."""
 
-    def __init__(self, prefix, gate_name, up_name, in_features, intermediate, dtype, std=0.02, suffixes=(".weight", ".bias")):
+    def __init__(self, prefix, gate_name, up_name, in_features, intermediate, dtype, std=0.02, suffixes=(".weight", ".bias"),
+                 epilogue="swiglu", epilogue_params=None):
+        """``epilogue``: the gated activation, "swiglu" or "glu_clamped" (with ``epilogue_params`` = (limit, alpha))."""
         super().__init__(prefix, [gate_name, up_name], in_features, [intermediate, intermediate], False, dtype, std, suffixes)
         self.intermediate = int(intermediate)
+        self.epilogue = epilogue
+        self.epilogue_values = tuple(float(v) for v in epilogue_params) if epilogue_params is not None else None
+        self.epilogue_params = None                     # the values on the device, made when the weights are bound
         self.fused_activation = dtype == torch.bfloat16 and intermediate % 8 == 0 and in_features % 8 == 0
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -93,15 +98,20 @@ class GateUpLinear(FusedLinear):
         gate = tensors.pop(f"{self.prefix}{self.names[0]}{self.w_suffix}")
         up = tensors.pop(f"{self.prefix}{self.names[1]}{self.w_suffix}")
         self.weight = K.interleave_gate_up(gate, up)
+        if self.epilogue_values is not None:
+            self.epilogue_params = torch.tensor(self.epilogue_values, dtype=torch.float32, device=self.weight.device)
 
     def activation(self, x: torch.Tensor) -> torch.Tensor:
         """up(x) * silu(gate(x)), [tokens, intermediate]."""
         if self.fused_activation:
             x, row_scale = undefer(x, self.weight)
             act = torch.empty((x.shape[0], self.intermediate), dtype=self.dtype, device=x.device)
-            K.linear(x, self.weight, None, act, epilogue="swiglu", row_scale=row_scale)
+            K.linear(x, self.weight, None, act, epilogue=self.epilogue, row_scale=row_scale, epilogue_params=self.epilogue_params)
         else:
             both = self(x)                                 # x may be deferred: the product multiplies its factor out
             act = torch.empty((both.shape[0], self.intermediate), dtype=self.dtype, device=both.device)
-            K.swiglu(both, act)
+            if self.epilogue == "swiglu":
+                K.swiglu(both, act)
+            else:
+                K.glu_clamped(both, act, *self.epilogue_values)
         return act

@@ -21,6 +21,7 @@ from .. import kernels as K
 from ..weights.loader import ParamSpec
 from .base import MIXERS, FixedState, Mixer
 from .linear import FusedLinear
+from .scan import scan_chunks
 
 
 @MIXERS.register("decay_linear_attention")
@@ -64,7 +65,7 @@ class DecayLinearAttention(Mixer):
         qk, vv = self.heads * self.dim, self.heads * self.value_dim
         proj = self.qkvg(h)
         o32 = torch.empty((T, vv), dtype=torch.float32, device=h.device)
-        K.decay_scan(proj, 0, qk, 2 * qk, self.decay, cache.state, ctx.q_start, ctx.state_slots, o32, self.heads, self.dim, self.value_dim)
+        K.decay_scan(proj, 0, qk, 2 * qk, self.decay, cache.state, ctx.q_start, ctx.state_slots, o32, self.heads, self.dim, self.value_dim, chunks=scan_chunks(ctx))
         y = torch.empty((T, vv), dtype=self.dtype, device=h.device)
         K.gated_rmsnorm(o32, proj, 2 * qk + vv, self.norm_weight, self.eps, 1, False, y)
         return self.out(y)

@@ -51,7 +51,8 @@ class SwiGLU(FeedForward):
 class ClampedGLU(FeedForward):
     """A gated feed-forward with bounded operands: g = min(gate(h), limit), u = clamp(up(h), -limit, limit),
     y = g * sigmoid(alpha * g) * (u + 1), output down(y); no biases.  ``limit`` and ``alpha`` are parameters of the spec.
-    gate and up are one product; the activation is computed in float32 and rounded once."""
+    gate and up are one product; the activation is computed in float32 and rounded once; in bfloat16 it is the epilogue
+    of that product."""
 
     def __init__(self, spec, prefix, dtype, device):
         super().__init__(spec, prefix, dtype, device)
@@ -61,8 +62,8 @@ class ClampedGLU(FeedForward):
         self.alpha = float(spec.get("alpha", 1.702))
         names = spec.get("names", {})
         suffixes = tuple(spec.get("suffixes", (".weight", ".bias")))
-        self.gate_up = FusedLinear(prefix, [names.get("gate", "gate_proj"), names.get("up", "up_proj")], self.hidden,
-                                   [self.intermediate, self.intermediate], False, dtype, suffixes=suffixes)
+        self.gate_up = GateUpLinear(prefix, names.get("gate", "gate_proj"), names.get("up", "up_proj"), self.hidden, self.intermediate, dtype,
+                                    suffixes=suffixes, epilogue="glu_clamped", epilogue_params=(self.limit, self.alpha))
         self.down = FusedLinear(prefix, [names.get("down", "down_proj")], self.intermediate, [self.hidden], False, dtype, suffixes=suffixes)
 
     def params(self) -> List[ParamSpec]:
@@ -73,7 +74,4 @@ class ClampedGLU(FeedForward):
         self.down.bind(tensors)
 
     def forward(self, h, ctx):
-        both = self.gate_up(h)
-        act = torch.empty((both.shape[0], self.intermediate), dtype=self.dtype, device=both.device)
-        K.glu_clamped(both, act, self.limit, self.alpha)
-        return self.down(act)
+        return self.down(self.gate_up.activation(h))

@@ -35,10 +35,13 @@ class ParallelMixer(Mixer):
         it = iter(cache.parts)
         return [next(it) if m.cache_requirement() is not None else None for m in (self.left, self.right)]
 
-    def forward(self, h, ctx, cache):
+    # forward_pair: the two outputs and their factors as they are, for a block whose write-back takes the sum in
+    # (parts.block.HyperPreNormBlock); forward: the sum itself
+    produces_pairs = True
+
+    def forward_pair(self, h, ctx, cache) -> "K.WeightedPair":
         cl, cr = self._caches(cache)
-        a = self.left.forward(h, ctx, cl)
-        b = self.right.forward(h, ctx, cr)
-        out = torch.empty_like(a)
-        K.weighted_sum2(a, b, self.left_scale, self.right_scale, out)
-        return out
+        return K.WeightedPair(self.left.forward(h, ctx, cl), self.right.forward(h, ctx, cr), self.left_scale, self.right_scale)
+
+    def forward(self, h, ctx, cache):
+        return self.forward_pair(h, ctx, cache).materialize()

@@ -24,6 +24,7 @@ from .. import kernels as K
 from ..weights.loader import ParamSpec
 from .base import MIXERS, FixedState, Mixer
 from .linear import FusedLinear
+from .scan import scan_chunks
 
 
 @MIXERS.register("selective_ssm")
@@ -87,7 +88,7 @@ class SelectiveStateSpace(Mixer):
         K.conv_state_shift(proj, self.inner, self.channels, self.taps, cache.state, self.scan_elements, ctx.q_start, ctx.state_slots)
         y32 = torch.empty((T, self.inner), dtype=torch.float32, device=h.device)
         K.ssm_scan(xbc, proj, self.inner + self.channels, self.dt_bias, self.A_log, self.D, cache.state, ctx.q_start, ctx.state_slots, y32,
-                   self.heads, self.head_dim, self.state_size, self.groups)
+                   self.heads, self.head_dim, self.state_size, self.groups, chunks=scan_chunks(ctx))
         y = torch.empty((T, self.inner), dtype=self.dtype, device=h.device)
         K.gated_rmsnorm(y32, proj, 0, self.norm_weight, self.eps, self.norm_groups, True, y)
         return self.out(y)

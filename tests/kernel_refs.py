@@ -47,7 +47,7 @@ def residual_add(x32, delta):
     x32.add_(delta.float())
 
 
-def linear(a, weight, bias, out, epilogue=None, row_scale=None):
+def linear(a, weight, bias, out, epilogue=None, row_scale=None, epilogue_params=None):
     y = a.float() @ weight.float().t()
     if row_scale is not None:
         y = y * _factor(row_scale)
@@ -59,6 +59,12 @@ def linear(a, weight, bias, out, epilogue=None, row_scale=None):
         y = y.view(M, N // 16, 2, 8)
         g, u = y[:, :, 0, :], y[:, :, 1, :]
         y = (u * (g / (1.0 + torch.exp(-g)))).reshape(M, N // 2)
+    elif epilogue == "glu_clamped":
+        M, N = y.shape
+        limit, alpha = (float(v) for v in epilogue_params.tolist())
+        y = y.view(M, N // 16, 2, 8)
+        g, u = torch.clamp(y[:, :, 0, :], max=limit), torch.clamp(y[:, :, 1, :], min=-limit, max=limit)
+        y = (g * torch.sigmoid(alpha * g) * (u + 1.0)).reshape(M, N // 2)
     _store(out, y)
 
 
@@ -252,6 +258,8 @@ def hc_read_norm(xs, in_w, rows, weight, eps, out):
 
 
 def hc_update(xs, y, mix, out_w, next_in=None, next_weight=None, eps=0.0, next_out=None):
+    if hasattr(y, "sa"):                                   # a pair that stands for sa * a + sb * b
+        y = y.sa * y.a.float() + y.sb * y.b.float()
     new = torch.einsum("sr,tsw->trw", mix, xs) + out_w[None, :, None] * y.float()[:, None, :]
     xs.copy_(new)
     if next_out is not None:
@@ -288,7 +296,8 @@ def conv_state_shift(x, col, channels, taps, state, state_off, q_start, slots):
         view.copy_(seq[-(taps - 1):])
 
 
-def ssm_scan(xbc, proj, dt_col, dt_bias, A_log, D, state, q_start, slots, y32, heads, head_dim, state_size, groups):
+def ssm_scan(xbc, proj, dt_col, dt_bias, A_log, D, state, q_start, slots, y32, heads, head_dim, state_size, groups, chunks=None):
+    # (chunks only says how a kernel shares the work out)
     starts, sl = q_start.tolist(), slots.tolist()
     inner, P, N = heads * head_dim, head_dim, state_size
     rate = torch.exp(A_log)
@@ -308,7 +317,7 @@ def ssm_scan(xbc, proj, dt_col, dt_bias, A_log, D, state, q_start, slots, y32, h
             y32[t] = (torch.einsum("hnp,hn->hp", S, Cm) + D[:, None] * x).reshape(inner)
 
 
-def decay_scan(qkv, q_col, k_col, v_col, decay, state, q_start, slots, out32, heads, dim, vdim):
+def decay_scan(qkv, q_col, k_col, v_col, decay, state, q_start, slots, out32, heads, dim, vdim, chunks=None):
     starts, sl = q_start.tolist(), slots.tolist()
     for s in range(len(starts) - 1):
         lo, hi = starts[s], starts[s + 1]

@@ -250,6 +250,25 @@ def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(dtype, de
     assert m.num_free_slots() == 3 and all(m.num_free_pages(g) == m.num_pages for g in range(len(m.groups)))
 
 
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_portions_of_several_requests_in_one_step(dtype, device, folders, request):
+    """Portions long enough for the scans to run in chunks (of 64 tokens, side by side), of requests that begin, go on and
+    decode in the same step: chunk borders in the middle of a portion, states carried over them and into the next step."""
+    dev = use_device(device, request)
+    folder, cfg, w = folders["mixed"]
+    lens = {"x": 333, "y": 140, "z": 205} if device == "cuda" else {"x": 150, "y": 130, "z": 140}
+    reqs = {r: random_tokens(n, cfg["vocab"], 70 + n) for r, n in lens.items()}
+    run = Run(folder, dtype, dev, 64 * 14)
+    run.step([("x", reqs["x"], 129), ("y", reqs["y"], 3)])
+    run.step([("x", reqs["x"], 1), ("y", reqs["y"], 128), ("z", reqs["z"], lens["z"] - 1)])
+    run.step([("x", reqs["x"], lens["x"] - 130), ("y", reqs["y"], 1), ("z", reqs["z"], 1)])
+    for _ in range(lens["y"] - 132):
+        run.step([("y", reqs["y"], 1)])
+    for r, toks in reqs.items():
+        assert_close(run.logits(r), oracle(cfg, w, toks, dtype), dtype, f"{r} of {len(toks)} tokens")
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding_from_captured_steps(dtype, folders):
