@@ -327,9 +327,10 @@ int launch_rope(const void* a, const void* w, const float* bias, void* out, int 
 
 }  // namespace
 
-// The fused q|k|v projection with rotary encoding and cache write in its epilogue, for few tokens.
+// The fused q|k|v projection with rotary encoding and cache write in its epilogue, for few tokens (rotary_dim 0, with no
+// denominators: nothing is rotated, the epilogue only writes the cache).
 bool li_gemv_rope_accepts(const void* a, const void* w, int M, int N, int K, int nh, int nkv, int dh, int rotary_dim) {
-    return M >= 1 && M <= kMaxM && K % 8 == 0 && dh % 16 == 0 && rotary_dim == dh && N == (nh + 2 * nkv) * dh &&
+    return M >= 1 && M <= kMaxM && K % 8 == 0 && dh % 16 == 0 && (rotary_dim == dh || rotary_dim == 0) && N == (nh + 2 * nkv) * dh &&
            ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0);
 }
 

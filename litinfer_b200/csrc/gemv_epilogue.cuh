@@ -43,7 +43,7 @@ __device__ __forceinline__ void store_rope(Get get, const float* __restrict__ bi
             x1 += bias[r1];
         }
         float y0 = x0, y1 = x1;
-        if (head < ra.nh + ra.nkv) {
+        if (ra.denom != nullptr && head < ra.nh + ra.nkv) {          // (no denominators: no rotation)
             float sn, cs;
             sincosf((float)ra.positions[tok] / ra.denom[jj], &sn, &cs);
             // q and k are rounded to bfloat16 by the projection before they are rotated, as in the unfused path

@@ -75,7 +75,7 @@ __global__ void conv_state_shift_kernel(const T* __restrict__ in, int in_stride,
 
 // The two recurrences walk a sequence's tokens in order, but every column of a head's state moves on by itself:
 // S[:, c] <- a_t S[:, c] + w_t[:] u_t[c],  out_t[c] = sum_i S[i, c] r_t[i].  So a column is the unit of work: eight lanes
-// hold it in registers (element i with lane i % 8), four columns share a warp, four warps a block; a block stages the
+// hold it in registers (four neighbouring elements at a time), four columns share a warp, 4 or 16 warps a block; a block stages the
 // vectors of kStage tokens that all its columns need (w, r, and the scalars) in shared memory once, with the
 // activations applied, and the columns then run through them with three shuffles a token for the sum.  The state is
 // stored column by column ([head][column][element]) so that it is read and written in whole lines.
@@ -89,8 +89,6 @@ __global__ void conv_state_shift_kernel(const T* __restrict__ in, int in_stride,
 // written to its slot: steps of single tokens and short portions.
 enum { kScanWhole = 0, kScanLocal = 1, kScanApply = 2 };
 constexpr int kStage = 16;          // tokens staged at a time
-constexpr int kColWarps = 4;        // warps a block
-constexpr int kCols = kColWarps * 4;
 
 __device__ __forceinline__ float oct_sum(float v) {
     v += __shfl_xor_sync(0xffffffffu, v, 1);
@@ -98,29 +96,46 @@ __device__ __forceinline__ float oct_sum(float v) {
     return v + __shfl_xor_sync(0xffffffffu, v, 4);
 }
 
-// xbc [T, C]: x (heads * P) | B (groups * N) | C (groups * N), after convolution and activation.  R = ceil(N / 8).
-template <typename T, int R>
-__global__ void __launch_bounds__(kColWarps * 32)
+// Which element of its column register k of lane m (of the eight lanes of a column) holds: four neighbours at a time, so
+// that the staged vectors are read with 16-byte loads, eight lanes a line.  The staged rows are padded with zeros to a
+// multiple of 32 elements, and so are the registers: the padding stays zero and adds nothing.
+__device__ __forceinline__ int element_of(int k, int m) { return 32 * (k >> 2) + 4 * m + (k & 3); }
+
+// One sequence or chunk of it: which tokens, whose slot, which chunk.
+struct Piece {
+    int q0, q1, slot, chunk;
+};
+__device__ __forceinline__ Piece piece_of(const int* __restrict__ seg, const int* __restrict__ q_start, const int* __restrict__ slots) {
+    Piece p;
+    if (seg) {
+        const int4 sg = reinterpret_cast<const int4*>(seg)[blockIdx.z];
+        p.q0 = sg.x; p.q1 = sg.y; p.chunk = sg.z; p.slot = sg.w;
+    } else {
+        p.q0 = q_start[blockIdx.z]; p.q1 = q_start[blockIdx.z + 1]; p.slot = slots[blockIdx.z]; p.chunk = 0;
+    }
+    return p;
+}
+
+// xbc [T, C]: x (heads * P) | B (groups * N) | C (groups * N), after convolution and activation.  R = 4 ceil(N / 32)
+// registers a lane; WARPS * 4 columns a block.
+template <typename T, int R, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, int dt_stride, const float* __restrict__ dt_bias,
                 const float* __restrict__ A_log, const float* __restrict__ D, float* __restrict__ state, long long state_stride,
                 const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ y, int heads, int P, int N, int groups,
                 const int* __restrict__ seg, int mode, float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
-    extern __shared__ float smem[];
-    float* Bs = smem;                           // [kStage][N]
-    float* Cs = Bs + (size_t)kStage * N;        // [kStage][N]
-    float* xs = Cs + (size_t)kStage * N;        // [kStage][kCols]
+    constexpr int NP = R * 8, kCols = WARPS * 4;           // padded row, columns of a block
+    extern __shared__ __align__(16) float smem[];
+    float* Bs = smem;                           // [kStage][NP]
+    float* Cs = Bs + kStage * NP;               // [kStage][NP]
+    float* xs = Cs + kStage * NP;               // [kStage][kCols]
     float* dts = xs + kStage * kCols;           // [kStage] step size
     float* das = dts + kStage;                  // [kStage] decay
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.y;
-    int q0, q1, slot, chunk = 0;
-    if (seg) {
-        const int4 sg = reinterpret_cast<const int4*>(seg)[blockIdx.z];
-        q0 = sg.x; q1 = sg.y; chunk = sg.z; slot = sg.w;
-    } else {
-        q0 = q_start[blockIdx.z]; q1 = q_start[blockIdx.z + 1]; slot = slots[blockIdx.z];
-    }
+    const Piece pc = piece_of(seg, q_start, slots);
+    const int q0 = pc.q0, q1 = pc.q1;
     if (q1 <= q0) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int m = lane & 7;
@@ -130,28 +145,28 @@ ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, 
     const int g = h / (heads / groups);
     const int inner = heads * P;
     const size_t col_at = ((size_t)h * P + (live ? c : 0)) * N;
-    float* st = state + (size_t)slot * state_stride + col_at;
-    float* cst = chunk_state ? chunk_state + (size_t)chunk * heads * P * N + col_at : nullptr;
+    float* st = state + (size_t)pc.slot * state_stride + col_at;
+    float* cst = chunk_state ? chunk_state + (size_t)pc.chunk * heads * P * N + col_at : nullptr;
     const float* from = mode == kScanWhole ? st : cst;
     float S[R];
 #pragma unroll
-    for (int k = 0; k < R; ++k) S[k] = (mode != kScanLocal && live && m + 8 * k < N) ? from[m + 8 * k] : 0.0f;
+    for (int k = 0; k < R; ++k) S[k] = (mode != kScanLocal && live && element_of(k, m) < N) ? from[element_of(k, m)] : 0.0f;
     const float rate = expf(A_log[h]), bias = dt_bias[h], skip = D[h];
     if (mode == kScanLocal && blockIdx.x == 0 && warp == 0) {
         // the chunk's decay as a whole, for the pass that carries states from chunk to chunk
         float sum = 0.0f;
         for (int t = q0 + lane; t < q1; t += 32) sum += -rate * softplus_f(to_float(dt_raw[(size_t)t * dt_stride + h]) + bias);
         sum = warp_sum(sum);
-        if (lane == 0) chunk_decay[(size_t)chunk * heads + h] = expf(sum);
+        if (lane == 0) chunk_decay[(size_t)pc.chunk * heads + h] = expf(sum);
     }
     for (int t0 = q0; t0 < q1; t0 += kStage) {
         const int nt = min(kStage, q1 - t0);
         __syncthreads();                                   // the stage before has been used up
-        for (int tk = warp; tk < nt; tk += kColWarps) {
+        for (int tk = warp; tk < nt; tk += WARPS) {
             const T* row = xbc + (size_t)(t0 + tk) * C;
-            for (int n = lane; n < N; n += 32) {
-                Bs[tk * N + n] = to_float(row[inner + g * N + n]);
-                Cs[tk * N + n] = to_float(row[inner + (groups + g) * N + n]);
+            for (int n = lane; n < NP; n += 32) {
+                Bs[tk * NP + n] = n < N ? to_float(row[inner + g * N + n]) : 0.0f;
+                Cs[tk * NP + n] = n < N ? to_float(row[inner + (groups + g) * N + n]) : 0.0f;
             }
         }
         for (int e = threadIdx.x; e < nt * kCols; e += blockDim.x) {
@@ -164,53 +179,55 @@ ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, 
             das[threadIdx.x] = expf(-rate * dt);
         }
         __syncthreads();
-#pragma unroll 4
+#pragma unroll 2
         for (int tk = 0; tk < nt; ++tk) {
             const float x = xs[tk * kCols + warp * 4 + (lane >> 3)];
             const float dx = dts[tk] * x, decay = das[tk];
-            const float* b = Bs + tk * N;
-            const float* cc = Cs + tk * N;
+            const float4* b4 = reinterpret_cast<const float4*>(Bs + tk * NP) + m;
+            const float4* c4 = reinterpret_cast<const float4*>(Cs + tk * NP) + m;
             float acc = 0.0f;
 #pragma unroll
-            for (int k = 0; k < R; ++k) {
-                const int n = m + 8 * k;
-                if (n < N) {
-                    S[k] = fmaf(decay, S[k], b[n] * dx);
-                    acc = fmaf(S[k], cc[n], acc);
-                }
+            for (int kk = 0; kk < R / 4; ++kk) {
+                const float4 b = b4[8 * kk], cc = c4[8 * kk];
+                S[4 * kk + 0] = fmaf(decay, S[4 * kk + 0], b.x * dx);
+                S[4 * kk + 1] = fmaf(decay, S[4 * kk + 1], b.y * dx);
+                S[4 * kk + 2] = fmaf(decay, S[4 * kk + 2], b.z * dx);
+                S[4 * kk + 3] = fmaf(decay, S[4 * kk + 3], b.w * dx);
+                acc = fmaf(S[4 * kk + 0], cc.x, acc);
+                acc = fmaf(S[4 * kk + 1], cc.y, acc);
+                acc = fmaf(S[4 * kk + 2], cc.z, acc);
+                acc = fmaf(S[4 * kk + 3], cc.w, acc);
             }
-            acc = oct_sum(acc);
-            if (mode != kScanLocal && live && m == 0) y[(size_t)(t0 + tk) * inner + h * P + c] = fmaf(skip, x, acc);
+            if (mode != kScanLocal) {
+                acc = oct_sum(acc);
+                if (live && m == 0) y[(size_t)(t0 + tk) * inner + h * P + c] = fmaf(skip, x, acc);
+            }
         }
     }
     if (live && mode != kScanApply) {
         float* to = mode == kScanWhole ? st : cst;
 #pragma unroll
         for (int k = 0; k < R; ++k)
-            if (m + 8 * k < N) to[m + 8 * k] = S[k];
+            if (element_of(k, m) < N) to[element_of(k, m)] = S[k];
     }
 }
 
-// q, k [T, stride] at columns q_off + h d, k_off + h d; v at v_off + h dv; all before their activation.  R = ceil(d / 8).
-template <typename T, int R>
-__global__ void __launch_bounds__(kColWarps * 32)
+// q, k [T, stride] at columns q_off + h d, k_off + h d; v at v_off + h dv; all before their activation.
+template <typename T, int R, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 decay_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots,
                   float* __restrict__ out, int heads, int d, int dv, const int* __restrict__ seg, int mode, float* __restrict__ chunk_state) {
-    extern __shared__ float smem[];
-    float* qs = smem;                           // [kStage][d]
-    float* ks = qs + (size_t)kStage * d;        // [kStage][d]
-    float* vs = ks + (size_t)kStage * d;        // [kStage][kCols]
+    constexpr int DP = R * 8, kCols = WARPS * 4;
+    extern __shared__ __align__(16) float smem[];
+    float* qs = smem;                           // [kStage][DP]
+    float* ks = qs + kStage * DP;               // [kStage][DP]
+    float* vs = ks + kStage * DP;               // [kStage][kCols]
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.y;
-    int q0, q1, slot, chunk = 0;
-    if (seg) {
-        const int4 sg = reinterpret_cast<const int4*>(seg)[blockIdx.z];
-        q0 = sg.x; q1 = sg.y; chunk = sg.z; slot = sg.w;
-    } else {
-        q0 = q_start[blockIdx.z]; q1 = q_start[blockIdx.z + 1]; slot = slots[blockIdx.z];
-    }
+    const Piece pc = piece_of(seg, q_start, slots);
+    const int q0 = pc.q0, q1 = pc.q1;
     if (q1 <= q0) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int m = lane & 7;
@@ -218,21 +235,21 @@ decay_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, i
     const int c = col0 + warp * 4 + (lane >> 3);
     const bool live = c < dv;
     const size_t col_at = ((size_t)h * dv + (live ? c : 0)) * d;
-    float* st = state + (size_t)slot * state_stride + col_at;
-    float* cst = chunk_state ? chunk_state + (size_t)chunk * heads * dv * d + col_at : nullptr;
+    float* st = state + (size_t)pc.slot * state_stride + col_at;
+    float* cst = chunk_state ? chunk_state + (size_t)pc.chunk * heads * dv * d + col_at : nullptr;
     const float* from = mode == kScanWhole ? st : cst;
     float S[R];
 #pragma unroll
-    for (int k = 0; k < R; ++k) S[k] = (mode != kScanLocal && live && m + 8 * k < d) ? from[m + 8 * k] : 0.0f;
+    for (int k = 0; k < R; ++k) S[k] = (mode != kScanLocal && live && element_of(k, m) < d) ? from[element_of(k, m)] : 0.0f;
     const float lam = decay[h];
     for (int t0 = q0; t0 < q1; t0 += kStage) {
         const int nt = min(kStage, q1 - t0);
         __syncthreads();
-        for (int tk = warp; tk < nt; tk += kColWarps) {
+        for (int tk = warp; tk < nt; tk += WARPS) {
             const T* row = qkv + (size_t)(t0 + tk) * stride;
-            for (int i = lane; i < d; i += 32) {
-                if (mode != kScanLocal) qs[tk * d + i] = silu_f(to_float(row[q_off + h * d + i]));
-                ks[tk * d + i] = silu_f(to_float(row[k_off + h * d + i]));
+            for (int i = lane; i < DP; i += 32) {
+                qs[tk * DP + i] = (mode != kScanLocal && i < d) ? silu_f(to_float(row[q_off + h * d + i])) : 0.0f;
+                ks[tk * DP + i] = i < d ? silu_f(to_float(row[k_off + h * d + i])) : 0.0f;
             }
         }
         for (int e = threadIdx.x; e < nt * kCols; e += blockDim.x) {
@@ -240,31 +257,44 @@ decay_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, i
             vs[e] = col0 + j < dv ? silu_f(to_float(qkv[(size_t)(t0 + tk) * stride + v_off + h * dv + col0 + j])) : 0.0f;
         }
         __syncthreads();
-#pragma unroll 4
+#pragma unroll 2
         for (int tk = 0; tk < nt; ++tk) {
             const float v = vs[tk * kCols + warp * 4 + (lane >> 3)];
-            const float* kk = ks + tk * d;
-            const float* qq = qs + tk * d;
+            const float4* k4 = reinterpret_cast<const float4*>(ks + tk * DP) + m;
+            const float4* q4 = reinterpret_cast<const float4*>(qs + tk * DP) + m;
             float acc = 0.0f;
+            if (mode == kScanLocal) {
 #pragma unroll
-            for (int k = 0; k < R; ++k) {
-                const int i = m + 8 * k;
-                if (i < d) {
-                    S[k] = fmaf(lam, S[k], kk[i] * v);
-                    acc = fmaf(S[k], qq[i], acc);
+                for (int kk = 0; kk < R / 4; ++kk) {
+                    const float4 a = k4[8 * kk];
+                    S[4 * kk + 0] = fmaf(lam, S[4 * kk + 0], a.x * v);
+                    S[4 * kk + 1] = fmaf(lam, S[4 * kk + 1], a.y * v);
+                    S[4 * kk + 2] = fmaf(lam, S[4 * kk + 2], a.z * v);
+                    S[4 * kk + 3] = fmaf(lam, S[4 * kk + 3], a.w * v);
                 }
+                continue;
             }
-            if (mode != kScanLocal) {
-                acc = oct_sum(acc);
-                if (live && m == 0) out[(size_t)(t0 + tk) * heads * dv + h * dv + c] = acc;
+#pragma unroll
+            for (int kk = 0; kk < R / 4; ++kk) {
+                const float4 a = k4[8 * kk], q = q4[8 * kk];
+                S[4 * kk + 0] = fmaf(lam, S[4 * kk + 0], a.x * v);
+                S[4 * kk + 1] = fmaf(lam, S[4 * kk + 1], a.y * v);
+                S[4 * kk + 2] = fmaf(lam, S[4 * kk + 2], a.z * v);
+                S[4 * kk + 3] = fmaf(lam, S[4 * kk + 3], a.w * v);
+                acc = fmaf(S[4 * kk + 0], q.x, acc);
+                acc = fmaf(S[4 * kk + 1], q.y, acc);
+                acc = fmaf(S[4 * kk + 2], q.z, acc);
+                acc = fmaf(S[4 * kk + 3], q.w, acc);
             }
+            acc = oct_sum(acc);
+            if (live && m == 0) out[(size_t)(t0 + tk) * heads * dv + h * dv + c] = acc;
         }
     }
     if (live && mode != kScanApply) {
         float* to = mode == kScanWhole ? st : cst;
 #pragma unroll
         for (int k = 0; k < R; ++k)
-            if (m + 8 * k < d) to[m + 8 * k] = S[k];
+            if (element_of(k, m) < d) to[element_of(k, m)] = S[k];
     }
 }
 
@@ -283,13 +313,24 @@ __global__ void scan_carry_kernel(float* __restrict__ state, long long state_str
     const int h = e / per_head;
     float* st = state + (size_t)slot * state_stride + e;
     float S = *st;
-    for (int c = first; c < first + count; ++c) {
-        float* z = chunk_state + (size_t)c * elements + e;
-        const float end_state = *z;
-        *z = S;
-        // the chunk's decay: given, or a constant per token and head to the power of the chunk's length
-        const float dec = chunk_decay ? chunk_decay[(size_t)c * heads + h] : powf(token_decay[h], (float)(seg[4 * c + 1] - seg[4 * c]));
-        S = fmaf(dec, S, end_state);
+    for (int c0 = first; c0 < first + count; c0 += 8) {
+        // eight chunks' end states and decays are asked for at once: they do not depend on S
+        float z[8], dec[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int c = c0 + u;
+            const bool in = c < first + count;
+            z[u] = in ? chunk_state[(size_t)c * elements + e] : 0.0f;
+            // the chunk's decay: given, or a constant per token and head to the power of the chunk's length
+            dec[u] = !in ? 1.0f : chunk_decay ? chunk_decay[(size_t)c * heads + h] : powf(token_decay[h], (float)(seg[4 * c + 1] - seg[4 * c]));
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (c0 + u < first + count) {
+                chunk_state[(size_t)(c0 + u) * elements + e] = S;
+                S = fmaf(dec[u], S, z[u]);
+            }
+        }
     }
     *st = S;
 }
@@ -365,17 +406,29 @@ LI_EXPORT int li_conv_state_shift(const void* in, int dtype, int in_stride, int 
     return li_check_launch("conv_state_shift");
 }
 
-template <typename T, int R>
-static int launch_ssm(const void* xbc, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log, const float* D,
+template <typename T, int R, int WARPS>
+static int launch_ssm_w(const void* xbc, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log, const float* D,
                       float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads, int P, int N,
                       int groups, const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream) {
-    const size_t smem = ((size_t)2 * kStage * N + kStage * kCols + 2 * kStage) * sizeof(float);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaError_t e = li_launch_pdl(ssm_scan_kernel<T, R>, dim3(ceil_div(P, kCols), heads, S), dim3(kColWarps * 32), smem, stream, (const T*)xbc, C,
+    const size_t smem = ((size_t)2 * kStage * R * 8 + kStage * WARPS * 4 + 2 * kStage) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<T, R, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = li_launch_pdl(ssm_scan_kernel<T, R, WARPS>, dim3(ceil_div(P, WARPS * 4), heads, S), dim3(WARPS * 32), smem, stream, (const T*)xbc, C,
                                   (const T*)dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, heads, P, N, groups, seg, mode,
                                   chunk_state, chunk_decay);
     if (e != cudaSuccess) return li_fail("ssm_scan: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("ssm_scan");
+}
+
+// Heads of at least 64 columns: 16 warps a block, so that what a block stages serves many columns; else 4.
+template <typename T, int R>
+static int launch_ssm(const void* xbc, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log, const float* D,
+                      float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads, int P, int N,
+                      int groups, const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream) {
+    if (P >= 64)
+        return launch_ssm_w<T, R, 16>(xbc, C, dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, S, heads, P, N, groups, seg,
+                                      mode, chunk_state, chunk_decay, stream);
+    return launch_ssm_w<T, R, 4>(xbc, C, dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, S, heads, P, N, groups, seg, mode,
+                                 chunk_state, chunk_decay, stream);
 }
 
 // The state of a slot: [heads][P][N] (a column of the head's N x P matrix at a time).
@@ -395,7 +448,6 @@ LI_EXPORT int li_ssm_scan(const void* xbc, int dtype, int C, const void* dt_raw,
                                                    P, N, groups, seg, mode, chunk_state, chunk_decay, stream)                                  \
                            : launch_ssm<bf16, RR>(xbc, C, dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, S, heads,  \
                                                   P, N, groups, seg, mode, chunk_state, chunk_decay, stream)
-    if (N <= 16) { LI_SCAN(2); }
     if (N <= 32) { LI_SCAN(4); }
     if (N <= 64) { LI_SCAN(8); }
     if (N <= 128) { LI_SCAN(16); }
@@ -403,16 +455,27 @@ LI_EXPORT int li_ssm_scan(const void* xbc, int dtype, int C, const void* dt_raw,
 #undef LI_SCAN
 }
 
+template <typename T, int R, int WARPS>
+static int launch_decay_w(const void* qkv, int stride, int q_off, int k_off, int v_off, const float* decay, float* state, long long state_stride,
+                        const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv, const int* seg, int mode,
+                        float* chunk_state, cudaStream_t stream) {
+    const size_t smem = ((size_t)2 * kStage * R * 8 + kStage * WARPS * 4) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<T, R, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = li_launch_pdl(decay_scan_kernel<T, R, WARPS>, dim3(ceil_div(dv, WARPS * 4), heads, S), dim3(WARPS * 32), smem, stream, (const T*)qkv, stride,
+                                  q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, heads, d, dv, seg, mode, chunk_state);
+    if (e != cudaSuccess) return li_fail("decay_scan: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("decay_scan");
+}
+
 template <typename T, int R>
 static int launch_decay(const void* qkv, int stride, int q_off, int k_off, int v_off, const float* decay, float* state, long long state_stride,
                         const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv, const int* seg, int mode,
                         float* chunk_state, cudaStream_t stream) {
-    const size_t smem = ((size_t)2 * kStage * d + kStage * kCols) * sizeof(float);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaError_t e = li_launch_pdl(decay_scan_kernel<T, R>, dim3(ceil_div(dv, kCols), heads, S), dim3(kColWarps * 32), smem, stream, (const T*)qkv, stride,
-                                  q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, heads, d, dv, seg, mode, chunk_state);
-    if (e != cudaSuccess) return li_fail("decay_scan: launch failed: %s", cudaGetErrorString(e));
-    return li_check_launch("decay_scan");
+    if (dv >= 64)
+        return launch_decay_w<T, R, 16>(qkv, stride, q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, S, heads, d, dv, seg, mode,
+                                        chunk_state, stream);
+    return launch_decay_w<T, R, 4>(qkv, stride, q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, S, heads, d, dv, seg, mode,
+                                   chunk_state, stream);
 }
 
 // The state of a slot: [heads][dv][d] (a column of the head's d x dv matrix at a time).
@@ -430,7 +493,6 @@ LI_EXPORT int li_decay_scan(const void* qkv, int dtype, int stride, int q_off, i
                                                      d, dv, seg, mode, chunk_state, stream)                                                  \
                            : launch_decay<bf16, RR>(qkv, stride, q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, S, heads,  \
                                                     d, dv, seg, mode, chunk_state, stream)
-    if (d <= 16) { LI_SCAN(2); }
     if (d <= 32) { LI_SCAN(4); }
     if (d <= 64) { LI_SCAN(8); }
     if (d <= 128) { LI_SCAN(16); }
