@@ -16,10 +16,29 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kMaxStreams = 8;
 
+// four neighbouring elements at a time where the width allows (16-byte loads and stores of the streams)
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x), b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<const unsigned*>(&a);
+    r.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+__device__ __forceinline__ float4 fma4(float a, float4 x, float4 acc) {
+    return make_float4(fmaf(a, x.x, acc.x), fmaf(a, x.y, acc.y), fmaf(a, x.z, acc.z), fmaf(a, x.w, acc.w));
+}
+
 template <typename T>
 __global__ void hc_read_norm_kernel(const float* __restrict__ xs, const float* __restrict__ in_w, const int* __restrict__ rows,
                                     const float* __restrict__ w, float eps, T* __restrict__ out, int rows_in, int s, int H) {
-    extern __shared__ float u_row[];
+    extern __shared__ __align__(16) float u_row[];
     __shared__ float scratch[32];
     __shared__ float wi[kMaxStreams];
     pdl_launch_dependents();
@@ -50,7 +69,7 @@ __global__ void hc_update_kernel(float* __restrict__ xs, const T* __restrict__ y
                                  const float* __restrict__ mix, const float* __restrict__ out_w,
                                  const float* __restrict__ next_in, const float* __restrict__ next_w, float eps, T* __restrict__ next_out,
                                  int s, int H) {
-    extern __shared__ float u_row[];
+    extern __shared__ __align__(16) float u_row[];
     __shared__ float scratch[32];
     __shared__ float m[kMaxStreams * kMaxStreams], wo[kMaxStreams], wi[kMaxStreams];
     pdl_launch_dependents();
@@ -64,34 +83,73 @@ __global__ void hc_update_kernel(float* __restrict__ xs, const T* __restrict__ y
     const int t = blockIdx.x;
     float* x = xs + (size_t)t * s * H;
     float ss = 0.0f;
-    for (int j = threadIdx.x; j < H; j += blockDim.x) {
-        float old[kMaxStreams];
+    if ((H & 3) == 0) {
+        for (int j = 4 * threadIdx.x; j < H; j += 4 * blockDim.x) {
+            float4 old[kMaxStreams];
 #pragma unroll
-        for (int a = 0; a < kMaxStreams; ++a) old[a] = a < s ? x[(size_t)a * H + j] : 0.0f;
-        float yj = to_float(y[(size_t)t * H + j]);
-        if (y2) yj = fmaf(s1, yj, s2 * to_float(y2[(size_t)t * H + j]));        // the sublayer's output as a weighted sum of two
-        float u = 0.0f;
+            for (int a = 0; a < kMaxStreams; ++a) old[a] = a < s ? load4(x + (size_t)a * H + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 yj = load4(y + (size_t)t * H + j);
+            if (y2) {
+                const float4 b = load4(y2 + (size_t)t * H + j);
+                yj = make_float4(fmaf(s1, yj.x, s2 * b.x), fmaf(s1, yj.y, s2 * b.y), fmaf(s1, yj.z, s2 * b.z), fmaf(s1, yj.w, s2 * b.w));
+            }
+            float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int r = 0; r < kMaxStreams; ++r) {
-            if (r < s) {
-                float v = wo[r] * yj;
+            for (int r = 0; r < kMaxStreams; ++r) {
+                if (r < s) {
+                    float4 v = make_float4(wo[r] * yj.x, wo[r] * yj.y, wo[r] * yj.z, wo[r] * yj.w);
 #pragma unroll
-                for (int a = 0; a < kMaxStreams; ++a)
-                    if (a < s) v = fmaf(m[a * s + r], old[a], v);
-                x[(size_t)r * H + j] = v;
-                u = fmaf(wi[r], v, u);
+                    for (int a = 0; a < kMaxStreams; ++a)
+                        if (a < s) v = fma4(m[a * s + r], old[a], v);
+                    store4(x + (size_t)r * H + j, v);
+                    u = fma4(wi[r], v, u);
+                }
+            }
+            if (next_out) {
+                store4(u_row + j, u);
+                ss += u.x * u.x;
+                ss += u.y * u.y;
+                ss += u.z * u.z;
+                ss += u.w * u.w;
             }
         }
-        if (next_out) {
-            u_row[j] = u;
-            ss += u * u;
+    } else {
+        for (int j = threadIdx.x; j < H; j += blockDim.x) {
+            float old[kMaxStreams];
+#pragma unroll
+            for (int a = 0; a < kMaxStreams; ++a) old[a] = a < s ? x[(size_t)a * H + j] : 0.0f;
+            float yj = to_float(y[(size_t)t * H + j]);
+            if (y2) yj = fmaf(s1, yj, s2 * to_float(y2[(size_t)t * H + j]));        // the sublayer's output as a weighted sum of two
+            float u = 0.0f;
+#pragma unroll
+            for (int r = 0; r < kMaxStreams; ++r) {
+                if (r < s) {
+                    float v = wo[r] * yj;
+#pragma unroll
+                    for (int a = 0; a < kMaxStreams; ++a)
+                        if (a < s) v = fmaf(m[a * s + r], old[a], v);
+                    x[(size_t)r * H + j] = v;
+                    u = fmaf(wi[r], v, u);
+                }
+            }
+            if (next_out) {
+                u_row[j] = u;
+                ss += u * u;
+            }
         }
     }
     if (!next_out) return;
     ss = block_sum(ss, scratch);
     const float rinv = 1.0f / sqrtf(ss / (float)H + eps);
     T* o = next_out + (size_t)t * H;
-    for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_float<T>((next_w[j] * u_row[j]) * rinv);
+    if ((H & 3) == 0) {
+        for (int j = 4 * threadIdx.x; j < H; j += 4 * blockDim.x) {
+            const float4 u = load4(u_row + j), w4 = load4(next_w + j);
+            store4(o + j, make_float4((w4.x * u.x) * rinv, (w4.y * u.y) * rinv, (w4.z * u.z) * rinv, (w4.w * u.w) * rinv));
+        }
+    } else {
+        for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_float<T>((next_w[j] * u_row[j]) * rinv);
+    }
 }
 
 __global__ void hc_expand_kernel(const float* __restrict__ x, float* __restrict__ xs, int s, int H) {

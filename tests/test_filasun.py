@@ -60,7 +60,7 @@ CONFIGS = {
     "window_only": config([parallel(ls=1.0, rs=0.0, ff=None)], width=32, vocab=61, streams=1),
     "decay_only": config([parallel(ls=0.0, rs=1.0, ff=None)], width=32, vocab=61, streams=2),
     "ssm_only": config([mamba(heads=3, vdim=8, state=6, conv=4)], width=40, vocab=50, streams=2),
-    "glu_only": config([mamba(heads=1, vdim=8, state=4, conv=1, ff=72, limit=0.25)], width=24, vocab=33, streams=4, cap=4.0),
+    "glu_only": config([mamba(heads=1, vdim=8, state=4, conv=1, ff=72, limit=0.25)], width=26, vocab=33, streams=4, cap=4.0),
 }
 
 
