@@ -102,7 +102,7 @@ def filasun_config(shape: str, layers: int, window: int = 1024):
                      "right": {"heads": nh, "dim": dh, "vdim": dh, "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, nh - 1)) for h in range(nh)]},
                      "left_scale": 0.7, "right_scale": 0.7}}
     ssm = {"type": "mamba2", "mlp": None, "mixer": {"heads": 2 * H // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}}
-    return {"architecture": "Filasun", "layers": [ssm if i % 3 == 2 else par for i in range(layers)], "logit_softcap": 30.0,
+    return {"architecture": "Filasun", "layers": [ssm if i % 3 == 2 else par for i in range(layers)], "logit_softcap": 25.0,
             "max_positions": d["max_position_embeddings"], "norm": {"eps": 1e-5}, "streams": 4, "vocab": d["vocab_size"], "width": H}
 
 

@@ -319,7 +319,7 @@ def _attention_case(K, dev, dtype, window, ctx, q_len, page_size, hot_distance, 
     slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / nh) for h in range(nh)], dtype=torch.float32, device=dev)
     gate = (0.5 * torch.randn(T, nh)).to(dev, dt)
     out = torch.empty(T, nh * dh, dtype=dt, device=dev)
-    K.paged_attention(qkv.to(dev, dt), out, **args, softcap=30.0, slopes=slopes, gate=gate, implementation=implementation)
+    K.paged_attention(qkv.to(dev, dt), out, **args, softcap=25.0, slopes=slopes, gate=gate, implementation=implementation)
     return out.float().cpu(), (q, k, v, gate.float().cpu(), slopes.cpu())
 
 
@@ -344,14 +344,14 @@ def test_keys_just_inside_and_just_outside_the_window(q_len, dtype, device, requ
     dev = use_device(device, request)
     from litinfer_b200 import kernels as K
 
-    window, page = 40, 16
+    window, page = 37, 16
     for ctx in ([75, 200] if device == "cuda" else [75]):
         if q_len > ctx:
             continue
         for hot, seen in ((window - 1, True), (window, False), (0, True), (window - 2, True), (window + 1, False), (15, True), (16, True)):
             out, (q, k, v, gate, slopes) = _attention_case(K, dev, dtype, window, ctx, q_len, page, hot)
             rnd = (lambda x: x.to(torch.bfloat16).float()) if dtype == "bfloat16" else (lambda x: x)
-            ref = _plain_attention(rnd(q), rnd(k), rnd(v), rnd(gate), slopes, window, 30.0)
+            ref = _plain_attention(rnd(q), rnd(k), rnd(v), rnd(gate), slopes, window, 25.0)
             tol = 2e-4 if dtype == "float32" else 0.03
             assert (out - ref).abs().max() <= tol * ref.abs().max(), f"ctx {ctx}, {q_len} tokens, hot key at distance {hot}"
             # the marker (10 (t + 1) in column 0 of the value) reaches the output only if the key is inside the window
