@@ -121,10 +121,10 @@ int li_add_position_rows(float* x, const void* table, int dtype, const int* posi
 /* ---- recurrent.cu: mixers with a state of fixed size per request (state [slots, state_stride] float) ---- */
 /* out[t, c] = silu(b[c] + sum_k w[c, k] in_(t - taps + 1 + k)[c]) over the C channels at column in_off of in [T,
  * in_stride]; inputs before a sequence's portion come from its state (the last taps - 1 inputs, oldest first, at
- * state_off). */
-int li_causal_conv_silu(const void* in, int dtype, int in_stride, int in_off, const float* w, const float* b, const float* state,
+ * state_off).  shift: every sequence has one token, and its state moves on in the same launch. */
+int li_causal_conv_silu(const void* in, int dtype, int in_stride, int in_off, const float* w, const float* b, float* state,
     long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
-    void* out, int T, int C, int taps, cudaStream_t stream);
+    void* out, int T, int C, int taps, int shift, cudaStream_t stream);
 
 /* Moves every sequence's convolution state on by its portion (after li_causal_conv_silu has read it). */
 int li_conv_state_shift(const void* in, int dtype, int in_stride, int in_off, float* state, long long state_stride, long long state_off,

@@ -29,8 +29,9 @@ constexpr int kMaxTaps = 8;
 // state [slots, state_stride] with the last taps - 1 inputs at state_off, oldest first, [taps - 1, C].
 template <typename T>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride, int in_off, const float* __restrict__ w, const float* __restrict__ b,
-                                        const float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ q_start,
-                                        const int* __restrict__ seq_of_token, const int* __restrict__ slots, T* __restrict__ out, int C, int taps) {
+                                        float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ q_start,
+                                        const int* __restrict__ seq_of_token, const int* __restrict__ slots, T* __restrict__ out, int C, int taps,
+                                        int shift) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.y;
@@ -39,7 +40,7 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride,
     const int s = seq_of_token[t];
     const int q0 = q_start[s];
     const int li = t - q0;
-    const float* st = state + (size_t)slots[s] * state_stride + state_off;
+    float* st = state + (size_t)slots[s] * state_stride + state_off;
     float acc = b[c];
     for (int k = 0; k < taps; ++k) {
         const int i = li - (taps - 1) + k;
@@ -47,6 +48,11 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride,
         acc = fmaf(w[(size_t)c * taps + k], v, acc);
     }
     out[(size_t)t * C + c] = from_float<T>(silu_f(acc));
+    if (shift) {
+        // a step of single tokens: nobody else reads this sequence's state, so it moves on here (oldest first)
+        for (int j = 0; j + 1 < taps; ++j)
+            st[(size_t)j * C + c] = j + 2 < taps ? st[(size_t)(j + 1) * C + c] : to_float(in[(size_t)t * in_stride + in_off + c]);
+    }
 }
 
 template <typename T>
@@ -366,9 +372,10 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ y, const T* __res
 
 }  // namespace
 
-LI_EXPORT int li_causal_conv_silu(const void* in, int dtype, int in_stride, int in_off, const float* w, const float* b, const float* state,
+// shift: every sequence of the step has one token (the caller's promise), and the state moves on in the same launch.
+LI_EXPORT int li_causal_conv_silu(const void* in, int dtype, int in_stride, int in_off, const float* w, const float* b, float* state,
                                   long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
-                                  void* out, int T, int C, int taps, cudaStream_t stream) {
+                                  void* out, int T, int C, int taps, int shift, cudaStream_t stream) {
     LI_REQUIRE(taps >= 1 && taps <= kMaxTaps, "causal convolution: %d taps (1..%d)", taps, kMaxTaps);
     LI_REQUIRE(C > 0 && in_off >= 0 && in_off + C <= in_stride, "causal convolution: %d channels at column %d of %d", C, in_off, in_stride);
     if (T == 0) return 0;
@@ -377,10 +384,10 @@ LI_EXPORT int li_causal_conv_silu(const void* in, int dtype, int in_stride, int 
     cudaError_t e;
     if (dtype == LI_F32)
         e = li_launch_pdl(causal_conv_silu_kernel<float>, grid, dim3(128), 0, stream, (const float*)in, in_stride, in_off, w, b, state, state_stride,
-                          state_off, q_start, seq_of_token, slots, (float*)out, C, taps);
+                          state_off, q_start, seq_of_token, slots, (float*)out, C, taps, shift);
     else if (dtype == LI_BF16)
         e = li_launch_pdl(causal_conv_silu_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)in, in_stride, in_off, w, b, state, state_stride,
-                          state_off, q_start, seq_of_token, slots, (bf16*)out, C, taps);
+                          state_off, q_start, seq_of_token, slots, (bf16*)out, C, taps, shift);
     else
         return li_fail("causal convolution: unknown dtype %d", dtype);
     if (e != cudaSuccess) return li_fail("causal convolution: launch failed: %s", cudaGetErrorString(e));

@@ -589,11 +589,12 @@ def _state_args(state: torch.Tensor, offset: int):
 
 
 def causal_conv_silu(x: torch.Tensor, col: int, weight: torch.Tensor, bias: torch.Tensor, state: torch.Tensor, state_off: int,
-                     q_start: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor, out: torch.Tensor) -> None:
+                     q_start: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, shift: bool = False) -> None:
     """Depthwise causal convolution and silu over the C channels at column ``col`` of ``x`` [T, *]:
     ``out[t, c] = silu(bias[c] + sum_k weight[c, k] * input_(t - taps + 1 + k)[c])``; inputs before a sequence's portion
     come from ``state[slot, state_off:]`` ([taps - 1, C], oldest first).  The state is not changed
-    (:func:`conv_state_shift` does that afterwards)."""
+    (:func:`conv_state_shift` does that afterwards), unless ``shift``: the caller promises that every sequence of the
+    step has one token, and the state moves on in the same launch."""
     T = x.shape[0]
     C, taps = weight.shape
     _need(x, "convolution input")
@@ -607,7 +608,7 @@ def causal_conv_silu(x: torch.Tensor, col: int, weight: torch.Tensor, bias: torc
     if state_off + (taps - 1) * C > state.shape[1]:
         raise KernelError("causal_conv_silu: the state is too small for the convolution's inputs")
     _check(library().li_causal_conv_silu(_p(x), _i(_dt(x)), _i(x.shape[1]), _i(col), _p(weight), _p(bias), st, stride, off, _p(q_start),
-                                         _p(seq_of_token), _p(slots), _p(out), _i(T), _i(C), _i(taps), _stream(out)), "causal_conv_silu")
+                                         _p(seq_of_token), _p(slots), _p(out), _i(T), _i(C), _i(taps), _i(1 if shift else 0), _stream(out)), "causal_conv_silu")
 
 
 def conv_state_shift(x: torch.Tensor, col: int, channels: int, taps: int, state: torch.Tensor, state_off: int, q_start: torch.Tensor,

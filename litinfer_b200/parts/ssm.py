@@ -83,9 +83,11 @@ class SelectiveStateSpace(Mixer):
         T = h.shape[0]
         proj = self.inp(h)
         xbc = torch.empty((T, self.channels), dtype=self.dtype, device=h.device)
+        single = ctx.max_q_len == 1                # a step of single tokens: the convolution moves its state on itself
         K.causal_conv_silu(proj, self.inner, self.conv_w, self.conv_b, cache.state, self.scan_elements, ctx.q_start, ctx.seq_of_token,
-                           ctx.state_slots, xbc)
-        K.conv_state_shift(proj, self.inner, self.channels, self.taps, cache.state, self.scan_elements, ctx.q_start, ctx.state_slots)
+                           ctx.state_slots, xbc, shift=single)
+        if not single:
+            K.conv_state_shift(proj, self.inner, self.channels, self.taps, cache.state, self.scan_elements, ctx.q_start, ctx.state_slots)
         y32 = torch.empty((T, self.inner), dtype=torch.float32, device=h.device)
         K.ssm_scan(xbc, proj, self.inner + self.channels, self.dt_bias, self.A_log, self.D, cache.state, ctx.q_start, ctx.state_slots, y32,
                    self.heads, self.head_dim, self.state_size, self.groups, chunks=scan_chunks(ctx))

@@ -270,7 +270,7 @@ def _silu(x):
     return x * torch.sigmoid(x)
 
 
-def causal_conv_silu(x, col, weight, bias, state, state_off, q_start, seq_of_token, slots, out):
+def causal_conv_silu(x, col, weight, bias, state, state_off, q_start, seq_of_token, slots, out, shift=False):
     C, taps = weight.shape
     starts, sl = q_start.tolist(), slots.tolist()
     for s in range(len(starts) - 1):
@@ -283,6 +283,8 @@ def causal_conv_silu(x, col, weight, bias, state, state_off, q_start, seq_of_tok
         for k in range(taps):
             acc += weight[:, k][None, :] * seq[k:k + hi - lo]
         _store(out[lo:hi], _silu(acc))
+    if shift:
+        conv_state_shift(x, col, C, taps, state, state_off, q_start, slots)
 
 
 def conv_state_shift(x, col, channels, taps, state, state_off, q_start, slots):

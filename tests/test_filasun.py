@@ -257,7 +257,7 @@ def test_long_portions_of_several_requests_in_one_step(dtype, device, folders, r
     decode in the same step: chunk borders in the middle of a portion, states carried over them and into the next step."""
     dev = use_device(device, request)
     folder, cfg, w = folders["mixed"]
-    lens = {"x": 333, "y": 140, "z": 205} if device == "cuda" else {"x": 150, "y": 130, "z": 140}
+    lens = {"x": 333, "y": 140, "z": 205} if device == "cuda" else {"x": 150, "y": 140, "z": 140}
     reqs = {r: random_tokens(n, cfg["vocab"], 70 + n) for r, n in lens.items()}
     run = Run(folder, dtype, dev, 64 * 14)
     run.step([("x", reqs["x"], 129), ("y", reqs["y"], 3)])
