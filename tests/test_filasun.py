@@ -360,6 +360,21 @@ def test_keys_just_inside_and_just_outside_the_window(q_len, dtype, device, requ
                 assert (last > 1.0) == seen, f"ctx {ctx}, {q_len} tokens: key at distance {hot} {'is' if seen else 'is not'} inside a window of {window}"
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("implementation,q_len", [("general", 1), ("general", 45), ("decode", 1), ("prefill", 7), ("prefill", 130)])
+def test_each_attention_kernel_alone_takes_the_changed_scores(implementation, q_len):
+    """The cap, the distance penalty and the head gate in each bfloat16 attention kernel by itself, over a context that
+    spans several pages and split units, with a hot key at the window's edge."""
+    from litinfer_b200 import kernels as K
+
+    dev, window = torch.device("cuda:0"), 300
+    for ctx, hot in ((700, window - 1), (700, window), (333, 5)):
+        out, (q, k, v, gate, slopes) = _attention_case(K, dev, "bfloat16", window, ctx, q_len, 16, hot, implementation=implementation)
+        rnd = lambda x: x.to(torch.bfloat16).float()
+        ref = _plain_attention(rnd(q), rnd(k), rnd(v), rnd(gate), slopes, window, 25.0)
+        assert (out - ref).abs().max() <= 0.03 * ref.abs().max(), f"{implementation}: ctx {ctx}, {q_len} tokens, hot key at distance {hot}"
+
+
 # --------------------------------------------------------------------------
 # a key far back, through the states
 # --------------------------------------------------------------------------
@@ -452,3 +467,158 @@ def test_random_weights_and_a_written_folder(tmp_path, cpu_kernels):
     run = Run(d, "float32", torch.device("cpu"), 64)
     run.step([("a", toks, 20)])
     assert_close(run.logits("a"), P.forward(cfg, w, toks).float(), "float32", "written folder")
+
+
+# --------------------------------------------------------------------------
+# each new kernel alone against its plain float32 reference (tests/kernel_refs.py)
+# --------------------------------------------------------------------------
+
+def _dt(dtype):
+    return torch.float32 if dtype == "float32" else torch.bfloat16
+
+
+def _close(a, b, dtype, what):
+    tol = 2e-5 if dtype == "float32" else 2e-2
+    assert (a.float() - b.float()).abs().max() <= tol * max(1.0, float(b.float().abs().max())), what
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,d,dv", [(3, 24, 40), (2, 128, 64), (1, 160, 72), (5, 8, 8)])
+def test_decay_scan_kernel(heads, d, dv, dtype):
+    import kernel_refs as R
+    from litinfer_b200 import kernels as K
+
+    dev, dt = torch.device("cuda:0"), _dt(dtype)
+    torch.manual_seed(heads * d + dv)
+    lens = [1, 200, 0, 67, 130]                                      # a single token, long portions, an empty sequence
+    q_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    T = sum(lens)
+    slots = torch.tensor([3, 0, 5, 1, 4], dtype=torch.int32, device=dev)
+    stride = 2 * heads * d + heads * dv + 7
+    qkv = torch.randn(T, stride, device=dev).to(dt)
+    decay = torch.tensor([0.5, 0.9, 0.99, 0.999, 0.95][:heads], dtype=torch.float32, device=dev)
+    state0 = 0.3 * torch.randn(6, heads * d * dv + 5, device=dev)
+    got_s, ref_s = state0.clone(), state0.clone()
+    ref_o = torch.zeros(T, heads * dv, device=dev)
+    R.decay_scan(qkv, 3, 3 + heads * d, 3 + 2 * heads * d, decay, ref_s, q_start, slots, ref_o, heads, d, dv)
+    for chunks in (None, K.ScanChunks(q_start.tolist(), slots.tolist(), dev)):
+        s, o = state0.clone(), torch.zeros(T, heads * dv, device=dev)
+        K.decay_scan(qkv, 3, 3 + heads * d, 3 + 2 * heads * d, decay, s, q_start, slots, o, heads, d, dv, chunks=chunks)
+        _close(o, ref_o, "float32", f"outputs, chunks {chunks is not None}")
+        _close(s, ref_s, "float32", f"states, chunks {chunks is not None}")
+        assert torch.equal(s[2], state0[2]) and torch.equal(s[:, -5:], state0[:, -5:]), "a slot nobody named, or the words behind the state, changed"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,P,N,groups", [(4, 24, 12, 2), (2, 64, 128, 1), (3, 66, 200, 3), (1, 8, 33, 1)])
+def test_ssm_scan_kernel(heads, P, N, groups, dtype):
+    import kernel_refs as R
+    from litinfer_b200 import kernels as K
+
+    dev, dt = torch.device("cuda:0"), _dt(dtype)
+    torch.manual_seed(heads * P + N)
+    lens = [130, 1, 0, 70, 1]
+    q_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    T = sum(lens)
+    slots = torch.tensor([2, 0, 1, 4, 3], dtype=torch.int32, device=dev)
+    C = heads * P + 2 * groups * N
+    xbc = (0.5 * torch.randn(T, C, device=dev)).to(dt)
+    proj = torch.randn(T, 5 + heads, device=dev).to(dt)
+    dt_bias, A_log, D = (0.5 * torch.randn(heads, device=dev) for _ in range(3))
+    state0 = 0.3 * torch.randn(5, heads * P * N + 9, device=dev)
+    ref_s, ref_y = state0.clone(), torch.zeros(T, heads * P, device=dev)
+    R.ssm_scan(xbc, proj, 5, dt_bias, A_log, D, ref_s, q_start, slots, ref_y, heads, P, N, groups)
+    for chunks in (None, K.ScanChunks(q_start.tolist(), slots.tolist(), dev)):
+        s, y = state0.clone(), torch.zeros(T, heads * P, device=dev)
+        K.ssm_scan(xbc, proj, 5, dt_bias, A_log, D, s, q_start, slots, y, heads, P, N, groups, chunks=chunks)
+        _close(y, ref_y, "float32", f"outputs, chunks {chunks is not None}")
+        _close(s, ref_s, "float32", f"states, chunks {chunks is not None}")
+        assert torch.equal(s[:, -9:], state0[:, -9:])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("taps", [1, 2, 4, 8])
+def test_convolution_kernels(taps, dtype):
+    import kernel_refs as R
+    from litinfer_b200 import kernels as K
+
+    dev, dt = torch.device("cuda:0"), _dt(dtype)
+    torch.manual_seed(taps)
+    C, col, off = 150, 11, 40
+    w, b = torch.randn(C, taps, device=dev), torch.randn(C, device=dev)
+    for lens in ([5, 1, 0, 2, 30], [1, 1, 1]):
+        q_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+        T = sum(lens)
+        seq = torch.repeat_interleave(torch.arange(len(lens)), torch.tensor(lens)).to(torch.int32).to(dev)
+        slots = torch.arange(len(lens), dtype=torch.int32, device=dev).flip(0).contiguous()
+        x = torch.randn(T, col + C + 3, device=dev).to(dt)
+        state0 = torch.randn(len(lens), off + (taps - 1) * C + 2, device=dev)
+        ref_s, ref_o = state0.clone(), torch.zeros(T, C, device=dev, dtype=dt)
+        R.causal_conv_silu(x, col, w, b, ref_s, off, q_start, seq, slots, ref_o)
+        R.conv_state_shift(x, col, C, taps, ref_s, off, q_start, slots)
+        for fused in ([False, True] if max(lens) == 1 else [False]):
+            s, o = state0.clone(), torch.zeros(T, C, device=dev, dtype=dt)
+            K.causal_conv_silu(x, col, w, b, s, off, q_start, seq, slots, o, shift=fused)
+            if not fused:
+                K.conv_state_shift(x, col, C, taps, s, off, q_start, slots)
+            _close(o, ref_o, dtype, f"outputs, fused {fused}")
+            _close(s, ref_s, "float32", f"states, fused {fused}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_stream_norm_and_gated_kernels(dtype):
+    import kernel_refs as R
+    from litinfer_b200 import kernels as K
+
+    dev, dt = torch.device("cuda:0"), _dt(dtype)
+    torch.manual_seed(4)
+    for T, s, H in ((37, 3, 100), (5, 1, 26), (64, 8, 256)):
+        xs0 = torch.randn(T, s, H, device=dev)
+        y, y2 = torch.randn(T, H, device=dev).to(dt), torch.randn(T, H, device=dev).to(dt)
+        mix, wo, wi, nw = torch.randn(s, s, device=dev), torch.randn(s, device=dev), torch.randn(s, device=dev), torch.randn(H, device=dev)
+        rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32, device=dev)
+        for read, rr in ((wi, None), (None, rows)):
+            a, b = (torch.empty((T if rr is None else 3, H), device=dev, dtype=dt) for _ in range(2))
+            K.hc_read_norm(xs0, read, rr, nw, 1e-5, a)
+            R.hc_read_norm(xs0, read, rr, nw, 1e-5, b)
+            _close(a, b, dtype, "read and norm")
+        for out, nxt in ((y, True), (K.WeightedPair(y, y2, 0.7, 1.3), True), (y, False)):
+            xa, xb = xs0.clone(), xs0.clone()
+            na, nb = (torch.empty(T, H, device=dev, dtype=dt) for _ in range(2))
+            K.hc_update(xa, out, mix, wo, wi if nxt else None, nw if nxt else None, 1e-5, na if nxt else None)
+            R.hc_update(xb, out, mix, wo, wi if nxt else None, nw if nxt else None, 1e-5, nb if nxt else None)
+            _close(xa, xb, "float32", "streams after the write-back")
+            if nxt:
+                _close(na, nb, dtype, "the next read")
+    for T, n, groups in ((33, 96, 3), (4, 50, 1)):
+        y32 = torch.randn(T, n, device=dev)
+        gate = torch.randn(T, n + 9, device=dev).to(dt)
+        w = torch.randn(n, device=dev)
+        for first in (True, False):
+            a, b = (torch.empty(T, n, device=dev, dtype=dt) for _ in range(2))
+            K.gated_rmsnorm(y32, gate, 4, w, 1e-5, groups, first, a)
+            R.gated_rmsnorm(y32, gate, 4, w, 1e-5, groups, first, b)
+            _close(a, b, dtype, f"gated norm, gate first {first}")
+    # the gated unit with bounded operands: as a kernel of its own and as the epilogue of every product kernel that has one
+    for M, I, Kd in ((5, 64, 96), (40, 136, 64), (300, 256, 128), (2048, 4096, 128)):          # (the last: the persistent tcgen05 product)
+        gate_w, up_w = (torch.randn(I, Kd, device=dev) / Kd ** 0.5 * 3 for _ in range(2))
+        a_in = torch.randn(M, Kd, device=dev).to(dt)
+        both = torch.empty(M, 2 * I, device=dev, dtype=dt)
+        K.linear(a_in, torch.cat([gate_w, up_w]).to(dt).contiguous(), None, both)
+        ref = torch.empty(M, I, device=dev, dtype=dt)
+        R.glu_clamped(both, ref, 0.8, 1.702)
+        got = torch.empty_like(ref)
+        K.glu_clamped(both, got, 0.8, 1.702)
+        _close(got, ref, dtype, "gated unit")
+        if dtype == "bfloat16":
+            params = torch.tensor([0.8, 1.702], dtype=torch.float32, device=dev)
+            inter = K.interleave_gate_up(gate_w.to(dt), up_w.to(dt))
+            for which in ("gemv", "gemv_tcgen05", "tcgen05"):
+                if (which != "tcgen05") == (M <= 64):
+                    fused = torch.empty_like(ref)
+                    K.linear_with(which, a_in, inter, None, fused, epilogue="glu_clamped", epilogue_params=params)
+                    _close(fused, ref, dtype, f"gated unit as the epilogue of {which}, {M} rows")
