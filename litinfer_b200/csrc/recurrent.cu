@@ -80,11 +80,13 @@ __global__ void conv_state_shift_kernel(const T* __restrict__ in, int in_stride,
 }
 
 // The two recurrences walk a sequence's tokens in order, but every column of a head's state moves on by itself:
-// S[:, c] <- a_t S[:, c] + w_t[:] u_t[c],  out_t[c] = sum_i S[i, c] r_t[i].  So a column is the unit of work: eight lanes
-// hold it in registers (four neighbouring elements at a time), four columns share a warp, 4 or 16 warps a block; a block stages the
-// vectors of kStage tokens that all its columns need (w, r, and the scalars) in shared memory once, with the
-// activations applied, and the columns then run through them with three shuffles a token for the sum.  The state is
-// stored column by column ([head][column][element]) so that it is read and written in whole lines.
+// S[:, c] <- a_t S[:, c] + w_t[:] u_t[c],  out_t[c] = sum_i S[i, c] r_t[i].  So a column is the unit of work.  A warp holds
+// eight columns in registers, each lane the same few neighbouring elements of all eight, so that one load of w and of r
+// from shared memory serves eight columns (with a column per eight lanes the kernel was bound by shared-memory wavefronts
+// and by the instructions around them: 127 a warp and token for four columns).  A block, up to 16 warps, stages the vectors
+// of kStage tokens that all its columns need (w, r, and the scalars) in shared memory once, with the activations applied.
+// The eight sums over the lanes take nine shuffles together.  The state is stored column by column
+// ([head][column][element]) so that it is read and written in whole lines.
 //
 // Long portions are cut into chunks that run side by side (a sequence alone has too few columns to fill the GPU, and a
 // walk over thousands of tokens is bound by its latency): `seg` names the chunks (begin, end, chunk, slot) and `mode` says
@@ -95,17 +97,6 @@ __global__ void conv_state_shift_kernel(const T* __restrict__ in, int in_stride,
 // written to its slot: steps of single tokens and short portions.
 enum { kScanWhole = 0, kScanLocal = 1, kScanApply = 2 };
 constexpr int kStage = 16;          // tokens staged at a time
-
-__device__ __forceinline__ float oct_sum(float v) {
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    return v + __shfl_xor_sync(0xffffffffu, v, 4);
-}
-
-// Which element of its column register k of lane m (of the eight lanes of a column) holds: four neighbours at a time, so
-// that the staged vectors are read with 16-byte loads, eight lanes a line.  The staged rows are padded with zeros to a
-// multiple of 32 elements, and so are the registers: the padding stays zero and adds nothing.
-__device__ __forceinline__ int element_of(int k, int m) { return 32 * (k >> 2) + 4 * m + (k & 3); }
 
 // One sequence or chunk of it: which tokens, whose slot, which chunk.
 struct Piece {
@@ -122,20 +113,55 @@ __device__ __forceinline__ Piece piece_of(const int* __restrict__ seg, const int
     return p;
 }
 
-// xbc [T, C]: x (heads * P) | B (groups * N) | C (groups * N), after convolution and activation.  R = 4 ceil(N / 32)
-// registers a lane; WARPS * 4 columns a block.
-template <typename T, int R, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
+constexpr int kWarpCols = 8;        // columns a warp walks
+
+// E neighbouring floats of a staged row (E = 1, 2, 4, 8), one load of up to 16 bytes at a time.
+template <int E>
+__device__ __forceinline__ void load_elements(float (&v)[E], const float* p) {
+    if constexpr (E == 1) {
+        v[0] = p[0];
+    } else if constexpr (E == 2) {
+        const float2 a = *reinterpret_cast<const float2*>(p);
+        v[0] = a.x; v[1] = a.y;
+    } else {
+#pragma unroll
+        for (int q = 0; q < E / 4; ++q) {
+            const float4 a = reinterpret_cast<const float4*>(p)[q];
+            v[4 * q] = a.x; v[4 * q + 1] = a.y; v[4 * q + 2] = a.z; v[4 * q + 3] = a.w;
+        }
+    }
+}
+
+// Sums over the 32 lanes of eight values a lane: each exchange halves the values a lane still carries, so nine shuffles
+// do for all eight.  Afterwards every lane holds the sum of value 4 (lane >> 4 & 1) + 2 (lane >> 3 & 1) + (lane >> 2 & 1).
+__device__ __forceinline__ float sum8_across_warp(const float (&a)[8], int lane) {
+    float b[4], c[2];
+    const bool up16 = lane & 16, up8 = lane & 8, up4 = lane & 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) b[j] = (up16 ? a[j + 4] : a[j]) + __shfl_xor_sync(0xffffffffu, up16 ? a[j] : a[j + 4], 16);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) c[j] = (up8 ? b[j + 2] : b[j]) + __shfl_xor_sync(0xffffffffu, up8 ? b[j] : b[j + 2], 8);
+    float v = (up4 ? c[1] : c[0]) + __shfl_xor_sync(0xffffffffu, up4 ? c[0] : c[1], 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v + __shfl_xor_sync(0xffffffffu, v, 1);
+}
+__device__ __forceinline__ int column_after_sum8(int lane) { return 4 * ((lane >> 4) & 1) + 2 * ((lane >> 3) & 1) + ((lane >> 2) & 1); }
+
+// xbc [T, C]: x (heads * P) | B (groups * N) | C (groups * N), after convolution and activation.  E = ceil(N / 32)
+// rounded up to 1, 2, 4 or 8 elements a lane; blockDim.x / 32 warps of eight columns each.
+template <typename T, int E>
+__global__ void __launch_bounds__(512)
 ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, int dt_stride, const float* __restrict__ dt_bias,
                 const float* __restrict__ A_log, const float* __restrict__ D, float* __restrict__ state, long long state_stride,
                 const int* __restrict__ q_start, const int* __restrict__ slots, float* __restrict__ y, int heads, int P, int N, int groups,
                 const int* __restrict__ seg, int mode, float* __restrict__ chunk_state, float* __restrict__ chunk_decay) {
-    constexpr int NP = R * 8, kCols = WARPS * 4;           // padded row, columns of a block
+    constexpr int NP = 32 * E;                         // a staged row, padded with zeros
+    const int warps = blockDim.x >> 5, cols = kWarpCols * warps;
     extern __shared__ __align__(16) float smem[];
     float* Bs = smem;                           // [kStage][NP]
     float* Cs = Bs + kStage * NP;               // [kStage][NP]
-    float* xs = Cs + kStage * NP;               // [kStage][kCols]
-    float* dts = xs + kStage * kCols;           // [kStage] step size
+    float* xs = Cs + kStage * NP;               // [kStage][cols]
+    float* dts = xs + kStage * cols;            // [kStage] step size
     float* das = dts + kStage;                  // [kStage] decay
     pdl_launch_dependents();
     pdl_wait();
@@ -144,19 +170,19 @@ ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, 
     const int q0 = pc.q0, q1 = pc.q1;
     if (q1 <= q0) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int m = lane & 7;
-    const int col0 = blockIdx.x * kCols;
-    const int c = col0 + warp * 4 + (lane >> 3);          // this lane's column of the head
-    const bool live = c < P;
+    const int col0 = blockIdx.x * cols + warp * kWarpCols;          // this warp's first column of the head
     const int g = h / (heads / groups);
     const int inner = heads * P;
-    const size_t col_at = ((size_t)h * P + (live ? c : 0)) * N;
-    float* st = state + (size_t)pc.slot * state_stride + col_at;
-    float* cst = chunk_state ? chunk_state + (size_t)pc.chunk * heads * P * N + col_at : nullptr;
+    const size_t head_at = (size_t)h * P * N;
+    float* st = state + (size_t)pc.slot * state_stride + head_at;
+    float* cst = chunk_state ? chunk_state + (size_t)pc.chunk * heads * P * N + head_at : nullptr;
     const float* from = mode == kScanWhole ? st : cst;
-    float S[R];
+    float S[kWarpCols][E];
 #pragma unroll
-    for (int k = 0; k < R; ++k) S[k] = (mode != kScanLocal && live && element_of(k, m) < N) ? from[element_of(k, m)] : 0.0f;
+    for (int j = 0; j < kWarpCols; ++j)
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+            S[j][e] = (mode != kScanLocal && col0 + j < P && E * lane + e < N) ? from[(size_t)(col0 + j) * N + E * lane + e] : 0.0f;
     const float rate = expf(A_log[h]), bias = dt_bias[h], skip = D[h];
     if (mode == kScanLocal && blockIdx.x == 0 && warp == 0) {
         // the chunk's decay as a whole, for the pass that carries states from chunk to chunk
@@ -168,16 +194,17 @@ ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, 
     for (int t0 = q0; t0 < q1; t0 += kStage) {
         const int nt = min(kStage, q1 - t0);
         __syncthreads();                                   // the stage before has been used up
-        for (int tk = warp; tk < nt; tk += WARPS) {
+        for (int tk = warp; tk < nt; tk += warps) {
             const T* row = xbc + (size_t)(t0 + tk) * C;
             for (int n = lane; n < NP; n += 32) {
                 Bs[tk * NP + n] = n < N ? to_float(row[inner + g * N + n]) : 0.0f;
-                Cs[tk * NP + n] = n < N ? to_float(row[inner + (groups + g) * N + n]) : 0.0f;
+                if (mode != kScanLocal) Cs[tk * NP + n] = n < N ? to_float(row[inner + (groups + g) * N + n]) : 0.0f;
             }
         }
-        for (int e = threadIdx.x; e < nt * kCols; e += blockDim.x) {
-            const int tk = e / kCols, j = e - tk * kCols;
-            xs[e] = col0 + j < P ? to_float(xbc[(size_t)(t0 + tk) * C + h * P + col0 + j]) : 0.0f;
+        for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
+            const int tk = e / cols, j = e - tk * cols;
+            const int c = blockIdx.x * cols + j;
+            xs[e] = c < P ? to_float(xbc[(size_t)(t0 + tk) * C + h * P + c]) : 0.0f;
         }
         if (threadIdx.x < nt) {
             const float dt = softplus_f(to_float(dt_raw[(size_t)(t0 + threadIdx.x) * dt_stride + h]) + bias);
@@ -187,48 +214,58 @@ ssm_scan_kernel(const T* __restrict__ xbc, int C, const T* __restrict__ dt_raw, 
         __syncthreads();
 #pragma unroll 2
         for (int tk = 0; tk < nt; ++tk) {
-            const float x = xs[tk * kCols + warp * 4 + (lane >> 3)];
-            const float dx = dts[tk] * x, decay = das[tk];
-            const float4* b4 = reinterpret_cast<const float4*>(Bs + tk * NP) + m;
-            const float4* c4 = reinterpret_cast<const float4*>(Cs + tk * NP) + m;
-            float acc = 0.0f;
+            float b[E], x[kWarpCols];
+            load_elements<E>(b, Bs + tk * NP + E * lane);
+            load_elements<kWarpCols>(x, xs + tk * cols + warp * kWarpCols);
+            const float dt = dts[tk], decay = das[tk];
+            if (mode == kScanLocal) {
 #pragma unroll
-            for (int kk = 0; kk < R / 4; ++kk) {
-                const float4 b = b4[8 * kk], cc = c4[8 * kk];
-                S[4 * kk + 0] = fmaf(decay, S[4 * kk + 0], b.x * dx);
-                S[4 * kk + 1] = fmaf(decay, S[4 * kk + 1], b.y * dx);
-                S[4 * kk + 2] = fmaf(decay, S[4 * kk + 2], b.z * dx);
-                S[4 * kk + 3] = fmaf(decay, S[4 * kk + 3], b.w * dx);
-                acc = fmaf(S[4 * kk + 0], cc.x, acc);
-                acc = fmaf(S[4 * kk + 1], cc.y, acc);
-                acc = fmaf(S[4 * kk + 2], cc.z, acc);
-                acc = fmaf(S[4 * kk + 3], cc.w, acc);
+                for (int j = 0; j < kWarpCols; ++j) {
+                    const float dx = dt * x[j];
+#pragma unroll
+                    for (int e = 0; e < E; ++e) S[j][e] = fmaf(decay, S[j][e], b[e] * dx);
+                }
+                continue;
             }
-            if (mode != kScanLocal) {
-                acc = oct_sum(acc);
-                if (live && m == 0) y[(size_t)(t0 + tk) * inner + h * P + c] = fmaf(skip, x, acc);
+            float cc[E], acc[kWarpCols];
+            load_elements<E>(cc, Cs + tk * NP + E * lane);
+#pragma unroll
+            for (int j = 0; j < kWarpCols; ++j) {
+                const float dx = dt * x[j];
+                acc[j] = 0.0f;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    S[j][e] = fmaf(decay, S[j][e], b[e] * dx);
+                    acc[j] = fmaf(S[j][e], cc[e], acc[j]);
+                }
             }
+            const float total = sum8_across_warp(acc, lane);
+            const int j = column_after_sum8(lane);
+            if ((lane & 3) == 0 && col0 + j < P) y[(size_t)(t0 + tk) * inner + h * P + col0 + j] = fmaf(skip, xs[tk * cols + warp * kWarpCols + j], total);
         }
     }
-    if (live && mode != kScanApply) {
+    if (mode != kScanApply) {
         float* to = mode == kScanWhole ? st : cst;
 #pragma unroll
-        for (int k = 0; k < R; ++k)
-            if (element_of(k, m) < N) to[element_of(k, m)] = S[k];
+        for (int j = 0; j < kWarpCols; ++j)
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+                if (col0 + j < P && E * lane + e < N) to[(size_t)(col0 + j) * N + E * lane + e] = S[j][e];
     }
 }
 
 // q, k [T, stride] at columns q_off + h d, k_off + h d; v at v_off + h dv; all before their activation.
-template <typename T, int R, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
+template <typename T, int E>
+__global__ void __launch_bounds__(512)
 decay_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, int v_off, const float* __restrict__ decay,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ q_start, const int* __restrict__ slots,
                   float* __restrict__ out, int heads, int d, int dv, const int* __restrict__ seg, int mode, float* __restrict__ chunk_state) {
-    constexpr int DP = R * 8, kCols = WARPS * 4;
+    constexpr int DP = 32 * E;
+    const int warps = blockDim.x >> 5, cols = kWarpCols * warps;
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;                           // [kStage][DP]
     float* ks = qs + kStage * DP;               // [kStage][DP]
-    float* vs = ks + kStage * DP;               // [kStage][kCols]
+    float* vs = ks + kStage * DP;               // [kStage][cols]
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.y;
@@ -236,71 +273,69 @@ decay_scan_kernel(const T* __restrict__ qkv, int stride, int q_off, int k_off, i
     const int q0 = pc.q0, q1 = pc.q1;
     if (q1 <= q0) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int m = lane & 7;
-    const int col0 = blockIdx.x * kCols;
-    const int c = col0 + warp * 4 + (lane >> 3);
-    const bool live = c < dv;
-    const size_t col_at = ((size_t)h * dv + (live ? c : 0)) * d;
-    float* st = state + (size_t)pc.slot * state_stride + col_at;
-    float* cst = chunk_state ? chunk_state + (size_t)pc.chunk * heads * dv * d + col_at : nullptr;
+    const int col0 = blockIdx.x * cols + warp * kWarpCols;
+    const size_t head_at = (size_t)h * dv * d;
+    float* st = state + (size_t)pc.slot * state_stride + head_at;
+    float* cst = chunk_state ? chunk_state + (size_t)pc.chunk * heads * dv * d + head_at : nullptr;
     const float* from = mode == kScanWhole ? st : cst;
-    float S[R];
+    float S[kWarpCols][E];
 #pragma unroll
-    for (int k = 0; k < R; ++k) S[k] = (mode != kScanLocal && live && element_of(k, m) < d) ? from[element_of(k, m)] : 0.0f;
+    for (int j = 0; j < kWarpCols; ++j)
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+            S[j][e] = (mode != kScanLocal && col0 + j < dv && E * lane + e < d) ? from[(size_t)(col0 + j) * d + E * lane + e] : 0.0f;
     const float lam = decay[h];
     for (int t0 = q0; t0 < q1; t0 += kStage) {
         const int nt = min(kStage, q1 - t0);
         __syncthreads();
-        for (int tk = warp; tk < nt; tk += WARPS) {
+        for (int tk = warp; tk < nt; tk += warps) {
             const T* row = qkv + (size_t)(t0 + tk) * stride;
             for (int i = lane; i < DP; i += 32) {
-                qs[tk * DP + i] = (mode != kScanLocal && i < d) ? silu_f(to_float(row[q_off + h * d + i])) : 0.0f;
+                if (mode != kScanLocal) qs[tk * DP + i] = i < d ? silu_f(to_float(row[q_off + h * d + i])) : 0.0f;
                 ks[tk * DP + i] = i < d ? silu_f(to_float(row[k_off + h * d + i])) : 0.0f;
             }
         }
-        for (int e = threadIdx.x; e < nt * kCols; e += blockDim.x) {
-            const int tk = e / kCols, j = e - tk * kCols;
-            vs[e] = col0 + j < dv ? silu_f(to_float(qkv[(size_t)(t0 + tk) * stride + v_off + h * dv + col0 + j])) : 0.0f;
+        for (int e = threadIdx.x; e < nt * cols; e += blockDim.x) {
+            const int tk = e / cols, j = e - tk * cols;
+            const int c = blockIdx.x * cols + j;
+            vs[e] = c < dv ? silu_f(to_float(qkv[(size_t)(t0 + tk) * stride + v_off + h * dv + c])) : 0.0f;
         }
         __syncthreads();
 #pragma unroll 2
         for (int tk = 0; tk < nt; ++tk) {
-            const float v = vs[tk * kCols + warp * 4 + (lane >> 3)];
-            const float4* k4 = reinterpret_cast<const float4*>(ks + tk * DP) + m;
-            const float4* q4 = reinterpret_cast<const float4*>(qs + tk * DP) + m;
-            float acc = 0.0f;
+            float kk[E], v[kWarpCols];
+            load_elements<E>(kk, ks + tk * DP + E * lane);
+            load_elements<kWarpCols>(v, vs + tk * cols + warp * kWarpCols);
             if (mode == kScanLocal) {
 #pragma unroll
-                for (int kk = 0; kk < R / 4; ++kk) {
-                    const float4 a = k4[8 * kk];
-                    S[4 * kk + 0] = fmaf(lam, S[4 * kk + 0], a.x * v);
-                    S[4 * kk + 1] = fmaf(lam, S[4 * kk + 1], a.y * v);
-                    S[4 * kk + 2] = fmaf(lam, S[4 * kk + 2], a.z * v);
-                    S[4 * kk + 3] = fmaf(lam, S[4 * kk + 3], a.w * v);
-                }
+                for (int j = 0; j < kWarpCols; ++j)
+#pragma unroll
+                    for (int e = 0; e < E; ++e) S[j][e] = fmaf(lam, S[j][e], kk[e] * v[j]);
                 continue;
             }
+            float qq[E], acc[kWarpCols];
+            load_elements<E>(qq, qs + tk * DP + E * lane);
 #pragma unroll
-            for (int kk = 0; kk < R / 4; ++kk) {
-                const float4 a = k4[8 * kk], q = q4[8 * kk];
-                S[4 * kk + 0] = fmaf(lam, S[4 * kk + 0], a.x * v);
-                S[4 * kk + 1] = fmaf(lam, S[4 * kk + 1], a.y * v);
-                S[4 * kk + 2] = fmaf(lam, S[4 * kk + 2], a.z * v);
-                S[4 * kk + 3] = fmaf(lam, S[4 * kk + 3], a.w * v);
-                acc = fmaf(S[4 * kk + 0], q.x, acc);
-                acc = fmaf(S[4 * kk + 1], q.y, acc);
-                acc = fmaf(S[4 * kk + 2], q.z, acc);
-                acc = fmaf(S[4 * kk + 3], q.w, acc);
+            for (int j = 0; j < kWarpCols; ++j) {
+                acc[j] = 0.0f;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    S[j][e] = fmaf(lam, S[j][e], kk[e] * v[j]);
+                    acc[j] = fmaf(S[j][e], qq[e], acc[j]);
+                }
             }
-            acc = oct_sum(acc);
-            if (live && m == 0) out[(size_t)(t0 + tk) * heads * dv + h * dv + c] = acc;
+            const float total = sum8_across_warp(acc, lane);
+            const int j = column_after_sum8(lane);
+            if ((lane & 3) == 0 && col0 + j < dv) out[(size_t)(t0 + tk) * heads * dv + h * dv + col0 + j] = total;
         }
     }
-    if (live && mode != kScanApply) {
+    if (mode != kScanApply) {
         float* to = mode == kScanWhole ? st : cst;
 #pragma unroll
-        for (int k = 0; k < R; ++k)
-            if (element_of(k, m) < d) to[element_of(k, m)] = S[k];
+        for (int j = 0; j < kWarpCols; ++j)
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+                if (col0 + j < dv && E * lane + e < d) to[(size_t)(col0 + j) * d + E * lane + e] = S[j][e];
     }
 }
 
@@ -413,29 +448,24 @@ LI_EXPORT int li_conv_state_shift(const void* in, int dtype, int in_stride, int 
     return li_check_launch("conv_state_shift");
 }
 
-template <typename T, int R, int WARPS>
-static int launch_ssm_w(const void* xbc, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log, const float* D,
+// warps of a block: enough for the head's columns, at most 16
+static int scan_warps(int columns) {
+    const int w = ceil_div(columns, kWarpCols);
+    return w >= 16 ? 16 : w >= 8 ? 8 : w >= 4 ? 4 : w >= 2 ? 2 : 1;
+}
+
+template <typename T, int E>
+static int launch_ssm(const void* xbc, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log, const float* D,
                       float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads, int P, int N,
                       int groups, const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream) {
-    const size_t smem = ((size_t)2 * kStage * R * 8 + kStage * WARPS * 4 + 2 * kStage) * sizeof(float);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<T, R, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaError_t e = li_launch_pdl(ssm_scan_kernel<T, R, WARPS>, dim3(ceil_div(P, WARPS * 4), heads, S), dim3(WARPS * 32), smem, stream, (const T*)xbc, C,
+    const int warps = scan_warps(P), cols = warps * kWarpCols;
+    const size_t smem = ((size_t)2 * kStage * 32 * E + kStage * cols + 2 * kStage) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(ssm_scan_kernel<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = li_launch_pdl(ssm_scan_kernel<T, E>, dim3(ceil_div(P, cols), heads, S), dim3(warps * 32), smem, stream, (const T*)xbc, C,
                                   (const T*)dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, heads, P, N, groups, seg, mode,
                                   chunk_state, chunk_decay);
     if (e != cudaSuccess) return li_fail("ssm_scan: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("ssm_scan");
-}
-
-// Heads of at least 64 columns: 16 warps a block, so that what a block stages serves many columns; else 4.
-template <typename T, int R>
-static int launch_ssm(const void* xbc, int C, const void* dt_raw, int dt_stride, const float* dt_bias, const float* A_log, const float* D,
-                      float* state, long long state_stride, const int* q_start, const int* slots, float* y, int S, int heads, int P, int N,
-                      int groups, const int* seg, int mode, float* chunk_state, float* chunk_decay, cudaStream_t stream) {
-    if (P >= 64)
-        return launch_ssm_w<T, R, 16>(xbc, C, dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, S, heads, P, N, groups, seg,
-                                      mode, chunk_state, chunk_decay, stream);
-    return launch_ssm_w<T, R, 4>(xbc, C, dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, S, heads, P, N, groups, seg, mode,
-                                 chunk_state, chunk_decay, stream);
 }
 
 // The state of a slot: [heads][P][N] (a column of the head's N x P matrix at a time).
@@ -455,34 +485,24 @@ LI_EXPORT int li_ssm_scan(const void* xbc, int dtype, int C, const void* dt_raw,
                                                    P, N, groups, seg, mode, chunk_state, chunk_decay, stream)                                  \
                            : launch_ssm<bf16, RR>(xbc, C, dt_raw, dt_stride, dt_bias, A_log, D, state, state_stride, q_start, slots, y, S, heads,  \
                                                   P, N, groups, seg, mode, chunk_state, chunk_decay, stream)
-    if (N <= 32) { LI_SCAN(4); }
-    if (N <= 64) { LI_SCAN(8); }
-    if (N <= 128) { LI_SCAN(16); }
-    LI_SCAN(32);
+    if (N <= 32) { LI_SCAN(1); }
+    if (N <= 64) { LI_SCAN(2); }
+    if (N <= 128) { LI_SCAN(4); }
+    LI_SCAN(8);
 #undef LI_SCAN
 }
 
-template <typename T, int R, int WARPS>
-static int launch_decay_w(const void* qkv, int stride, int q_off, int k_off, int v_off, const float* decay, float* state, long long state_stride,
-                        const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv, const int* seg, int mode,
-                        float* chunk_state, cudaStream_t stream) {
-    const size_t smem = ((size_t)2 * kStage * R * 8 + kStage * WARPS * 4) * sizeof(float);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<T, R, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaError_t e = li_launch_pdl(decay_scan_kernel<T, R, WARPS>, dim3(ceil_div(dv, WARPS * 4), heads, S), dim3(WARPS * 32), smem, stream, (const T*)qkv, stride,
-                                  q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, heads, d, dv, seg, mode, chunk_state);
-    if (e != cudaSuccess) return li_fail("decay_scan: launch failed: %s", cudaGetErrorString(e));
-    return li_check_launch("decay_scan");
-}
-
-template <typename T, int R>
+template <typename T, int E>
 static int launch_decay(const void* qkv, int stride, int q_off, int k_off, int v_off, const float* decay, float* state, long long state_stride,
                         const int* q_start, const int* slots, float* out, int S, int heads, int d, int dv, const int* seg, int mode,
                         float* chunk_state, cudaStream_t stream) {
-    if (dv >= 64)
-        return launch_decay_w<T, R, 16>(qkv, stride, q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, S, heads, d, dv, seg, mode,
-                                        chunk_state, stream);
-    return launch_decay_w<T, R, 4>(qkv, stride, q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, S, heads, d, dv, seg, mode,
-                                   chunk_state, stream);
+    const int warps = scan_warps(dv), cols = warps * kWarpCols;
+    const size_t smem = ((size_t)2 * kStage * 32 * E + kStage * cols) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = li_launch_pdl(decay_scan_kernel<T, E>, dim3(ceil_div(dv, cols), heads, S), dim3(warps * 32), smem, stream, (const T*)qkv, stride,
+                                  q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, heads, d, dv, seg, mode, chunk_state);
+    if (e != cudaSuccess) return li_fail("decay_scan: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("decay_scan");
 }
 
 // The state of a slot: [heads][dv][d] (a column of the head's d x dv matrix at a time).
@@ -500,10 +520,10 @@ LI_EXPORT int li_decay_scan(const void* qkv, int dtype, int stride, int q_off, i
                                                      d, dv, seg, mode, chunk_state, stream)                                                  \
                            : launch_decay<bf16, RR>(qkv, stride, q_off, k_off, v_off, decay, state, state_stride, q_start, slots, out, S, heads,  \
                                                     d, dv, seg, mode, chunk_state, stream)
-    if (d <= 32) { LI_SCAN(4); }
-    if (d <= 64) { LI_SCAN(8); }
-    if (d <= 128) { LI_SCAN(16); }
-    LI_SCAN(32);
+    if (d <= 32) { LI_SCAN(1); }
+    if (d <= 64) { LI_SCAN(2); }
+    if (d <= 128) { LI_SCAN(4); }
+    LI_SCAN(8);
 #undef LI_SCAN
 }
 
