@@ -101,11 +101,13 @@ __device__ __forceinline__ float swiglu_of(float gate, float up) {
     else return up * (gate / (1.0f + expf(-gate)));
 }
 
-// The activation of a gated product's epilogue.  params null: SwiGLU.  Else {limit, alpha}: the gated unit with bounded
-// operands, g = min(gate, limit), u = clamp(up, -limit, limit), g / (1 + exp(-alpha g)) * (u + 1).
-template <typename Tout>
+// The activation of a gated product's epilogue, chosen when the kernel is compiled (an epilogue in which one warp works
+// through its row alone is bound by the length of this chain of instructions: a choice per element costs SwiGLU 2 % of a
+// decode step).  Not kClamped: SwiGLU.  kClamped, with params = {limit, alpha}: the gated unit with bounded operands,
+// g = min(gate, limit), u = clamp(up, -limit, limit), g / (1 + exp(-alpha g)) * (u + 1).
+template <typename Tout, bool kClamped>
 __device__ __forceinline__ float glu_of(float gate, float up, const float* __restrict__ params) {
-    if (params == nullptr) return swiglu_of<Tout>(gate, up);
+    if constexpr (!kClamped) return swiglu_of<Tout>(gate, up);
     const float limit = __ldg(params), alpha = __ldg(params + 1);
     const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
     if constexpr (sizeof(Tout) == 2) return __fdividef(g, 1.0f + fast_exp2(-1.4426950408889634f * alpha * g)) * (u + 1.0f);

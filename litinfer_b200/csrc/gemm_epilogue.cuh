@@ -4,9 +4,10 @@
 
 #include "common.cuh"
 
-// v: columns col0 .. col0 + 31 of row `row` of a w^T.  kSwiglu: the columns come as 8 gate, 8 up, 8 gate, 8 up and give 16
+// v: columns col0 .. col0 + 31 of row `row` of a w^T.  kSwiglu (1: SwiGLU, 2: the gated unit with bounded operands, whose
+// parameters the bias argument points at): the columns come as 8 gate, 8 up, 8 gate, 8 up and give 16
 // activations up * gate / (1 + exp(-gate)) (src/ops/swiglu/op.cpp:17-23) at columns col0 / 2 .. of a row of N / 2.
-template <typename Tout, bool kSwiglu>
+template <typename Tout, int kSwiglu>
 __device__ __forceinline__ void gemm_store_piece(int row, int col0, float (&v)[32], const float* __restrict__ bias, Tout* __restrict__ out,
                                                  int M, int N) {
     if (kSwiglu) {
@@ -20,7 +21,7 @@ __device__ __forceinline__ void gemm_store_piece(int row, int col0, float (&v)[3
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float gate = v[16 * h + i], up = v[16 * h + 8 + i];
-                    a16[8 * h + i] = glu_of<Tout>(gate, up, bias);          // (bias: null, or the clamped unit's parameters)
+                    a16[8 * h + i] = glu_of<Tout, kSwiglu == 2>(gate, up, bias);          // (bias: null, or the clamped unit's parameters)
                 }
             if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0 && sizeof(Tout) == 2) {
                 uint4* d4 = reinterpret_cast<uint4*>(dst);

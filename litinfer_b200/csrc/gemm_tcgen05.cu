@@ -168,7 +168,7 @@ __device__ __forceinline__ void rope_stage_table(float2* cs_sm, const float* __r
 template <bool kRope>
 __host__ __device__ constexpr int threads_of() { return kRope ? 320 : kThreads; }
 
-template <int BM, int BN, typename Tout, bool kSwiglu, bool kPair = false, bool kRope = false>
+template <int BM, int BN, typename Tout, int kSwiglu, bool kPair = false, bool kRope = false>
 __global__ void __launch_bounds__(threads_of<kRope>(), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, Tout* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag,
@@ -450,7 +450,7 @@ int split_workspace(size_t floats, SplitWorkspace** out) {
     return 0;
 }
 
-template <int BM, int BN, typename Tout, bool kSwiglu, bool kPair = false, bool kRope = false>
+template <int BM, int BN, typename Tout, int kSwiglu, bool kPair = false, bool kRope = false>
 int launch_tile(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, int ksplit = 1,
                 const RopeEpilogue& rope = RopeEpilogue{}) {
     EncodeTiledFn encode = nullptr;
@@ -486,7 +486,7 @@ int launch_tile(const void* a, const void* w, const float* bias, void* out, int 
 
 // 256 x 256 tiles where they still fill most of the GPU (measured: better from about 120 CTAs on), else 128 x 128.
 // tile: 0 chooses, 1 forces the small tile, 2 the large one (for tests and measurements).
-template <typename Tout, bool kSwiglu>
+template <typename Tout, int kSwiglu>
 int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, int tile) {
     const long long big_ctas = (long long)ceil_div(M, 256) * ceil_div(N, 256);
     const int nkb = ceil_div(K, BK);
@@ -621,9 +621,10 @@ int li_linear_tcgen05(const void* a, const void* w, const float* bias, void* out
     if (li_epilogue_is_gated(epilogue)) {
         LI_REQUIRE(N % 16 == 0 && li_epilogue_bias_ok(epilogue, bias) && dtype_out == LI_BF16,
                    "linear (tcgen05): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
-        return launch<bf16, true>(a, w, bias, out, M, N, K, stream, g_forced_tile);
+        return epilogue == LI_EPILOGUE_GLU_CLAMPED ? launch<bf16, 2>(a, w, bias, out, M, N, K, stream, g_forced_tile)
+                                                   : launch<bf16, 1>(a, w, bias, out, M, N, K, stream, g_forced_tile);
     }
-    if (dtype_out == LI_BF16) return launch<bf16, false>(a, w, bias, out, M, N, K, stream, g_forced_tile);
-    if (dtype_out == LI_F32) return launch<float, false>(a, w, bias, out, M, N, K, stream, g_forced_tile);
+    if (dtype_out == LI_BF16) return launch<bf16, 0>(a, w, bias, out, M, N, K, stream, g_forced_tile);
+    if (dtype_out == LI_F32) return launch<float, 0>(a, w, bias, out, M, N, K, stream, g_forced_tile);
     return li_fail("linear (tcgen05): unsupported output dtype %d", dtype_out);
 }

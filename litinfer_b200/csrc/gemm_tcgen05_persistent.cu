@@ -40,7 +40,7 @@ struct __align__(1024) Smem {
     unsigned tmem_base;
 };
 
-template <typename Tout, bool kSwiglu>
+template <typename Tout, int kSwiglu>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                                const float* __restrict__ bias, Tout* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag) {
@@ -155,7 +155,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     }
 }
 
-template <typename Tout, bool kSwiglu>
+template <typename Tout, int kSwiglu>
 int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
     EncodeTiledFn encode = nullptr;
     int *err_host = nullptr, *err_dev = nullptr;
@@ -201,9 +201,9 @@ int li_linear_tcgen05_persistent(const void* a, const void* w, const float* bias
     if (li_epilogue_is_gated(epilogue)) {
         LI_REQUIRE(N % 16 == 0 && li_epilogue_bias_ok(epilogue, bias) && dtype_out == LI_BF16,
                    "linear (tcgen05, persistent): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
-        return launch<bf16, true>(a, w, bias, out, M, N, K, stream);
+        return epilogue == LI_EPILOGUE_GLU_CLAMPED ? launch<bf16, 2>(a, w, bias, out, M, N, K, stream) : launch<bf16, 1>(a, w, bias, out, M, N, K, stream);
     }
-    if (dtype_out == LI_BF16) return launch<bf16, false>(a, w, bias, out, M, N, K, stream);
-    if (dtype_out == LI_F32) return launch<float, false>(a, w, bias, out, M, N, K, stream);
+    if (dtype_out == LI_BF16) return launch<bf16, 0>(a, w, bias, out, M, N, K, stream);
+    if (dtype_out == LI_F32) return launch<float, 0>(a, w, bias, out, M, N, K, stream);
     return li_fail("linear (tcgen05, persistent): unsupported output dtype %d", dtype_out);
 }

@@ -58,14 +58,14 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-enum { kEpiNone = 0, kEpiSwiglu = 1, kEpiRope = 2, kEpiAddScaled = 3 };
+enum { kEpiNone = 0, kEpiSwiglu = 1, kEpiRope = 2, kEpiAddScaled = 3, kEpiGluClamped = 4 };     // (the last: SwiGLU's layout, another activation)
 
 template <int NT, int WARPS, typename Tout, int kEpi>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const float* __restrict__ bias, Tout* __restrict__ out,
                  float* __restrict__ partial, unsigned* __restrict__ counters, int M, int N, int K, int ksplit, const RopeArgs rope,
                  const RowScale rs, const AddScaled add) {
-    constexpr bool kSwiglu = kEpi == kEpiSwiglu;
+    constexpr int kSwiglu = kEpi == kEpiSwiglu ? 1 : kEpi == kEpiGluClamped ? 2 : 0;
     extern __shared__ float red_raw[];                 // [WARPS][NT * 128]
     float (*red)[NT * 128] = reinterpret_cast<float (*)[NT * 128]>(red_raw);
     __shared__ int is_last;
@@ -353,7 +353,8 @@ int li_linear_gemv_bf16(const void* a, const void* w, const float* bias, void* o
     if (li_epilogue_is_gated(epilogue)) {
         LI_REQUIRE(N % 16 == 0 && li_epilogue_bias_ok(epilogue, bias) && dtype_out == LI_BF16,
                    "linear (gemv): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
-        return launch_nt<bf16, kEpiSwiglu>(a, w, bias, out, M, N, K, stream, rs);
+        return epilogue == LI_EPILOGUE_GLU_CLAMPED ? launch_nt<bf16, kEpiGluClamped>(a, w, bias, out, M, N, K, stream, rs)
+                                                   : launch_nt<bf16, kEpiSwiglu>(a, w, bias, out, M, N, K, stream, rs);
     }
     if (dtype_out == LI_BF16) return launch_nt<bf16, kEpiNone>(a, w, bias, out, M, N, K, stream, rs);
     if (dtype_out == LI_F32) return launch_nt<float, kEpiNone>(a, w, bias, out, M, N, K, stream, rs);

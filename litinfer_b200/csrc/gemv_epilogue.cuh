@@ -79,7 +79,7 @@ __device__ __forceinline__ void store_rope(Get get, const float* __restrict__ bi
 // kSwiglu: the weight rows of a tile are 8 gate rows followed by the 8 up rows of the same
 // outputs; the element and its partner 64 places further on give one activation
 // up * gate / (1 + exp(-gate)) (src/ops/swiglu/op.cpp:17-23), stored at column n0 / 2 + g.
-template <int NT, typename Tout, bool kSwiglu, typename Get>
+template <int NT, typename Tout, int kSwiglu, typename Get>
 __device__ __forceinline__ void store_elements(Get get, const float* __restrict__ bias, Tout* __restrict__ out, int n0, int M, int N,
                                                int tid, int nthreads, const float* rs_sm) {
     // rs_sm: a factor per token (the reciprocal root of an RMSNorm whose weights are already in the input), or nullptr
@@ -102,7 +102,7 @@ __device__ __forceinline__ void store_elements(Get get, const float* __restrict_
                 gate *= rs_sm[tok];
                 up *= rs_sm[tok];
             }
-            if (col < half_n && tok < M) out[(size_t)tok * half_n + col] = from_float<Tout>(glu_of<Tout>(gate, up, bias));
+            if (col < half_n && tok < M) out[(size_t)tok * half_n + col] = from_float<Tout>(glu_of<Tout, kSwiglu == 2>(gate, up, bias));
         }
     }
 }

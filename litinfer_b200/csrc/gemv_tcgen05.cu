@@ -82,7 +82,7 @@ __device__ __forceinline__ void tmem_ld<64>(unsigned taddr, float (&v)[64]) {
     }
 }
 
-enum { kEpiNone = 0, kEpiSwiglu = 1, kEpiAddScaled = 2 };
+enum { kEpiNone = 0, kEpiSwiglu = 1, kEpiAddScaled = 2, kEpiGluClamped = 3 };     // (the last: SwiGLU's layout, another activation)
 
 template <int BT, typename Tout, int kEpi>
 __global__ void __launch_bounds__(kThreads)
@@ -90,7 +90,7 @@ gemv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     const float* __restrict__ bias, Tout* __restrict__ out, float* __restrict__ partial,
                     unsigned* __restrict__ counters, int M, int N, int K, int ksplit, int* __restrict__ error_flag, const RowScale rs,
                     const AddScaled add) {
-    constexpr bool kSwiglu = kEpi == kEpiSwiglu, kAdd = kEpi == kEpiAddScaled;
+    constexpr bool kSwiglu = kEpi == kEpiSwiglu || kEpi == kEpiGluClamped, kAdd = kEpi == kEpiAddScaled;
     extern __shared__ unsigned char smem_raw[];
     Smem<BT>& sm = *reinterpret_cast<Smem<BT>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -270,7 +270,7 @@ gemv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         const float up = __shfl_down_sync(0xffffffffu, v[j], 8);
                         if (j < M && (lane & 8) == 0 && row + 8 < N) {
                             const float gate = v[j];
-                            out[(size_t)j * half_n + col] = from_float<Tout>(glu_of<Tout>(gate, up, bias));
+                            out[(size_t)j * half_n + col] = from_float<Tout>(glu_of<Tout, kEpi == kEpiGluClamped>(gate, up, bias));
                         }
                     }
                 }
@@ -376,7 +376,8 @@ int li_linear_gemv_tcgen05(const void* a, const void* w, const float* bias, void
     if (li_epilogue_is_gated(epilogue)) {
         LI_REQUIRE(N % 16 == 0 && li_epilogue_bias_ok(epilogue, bias) && dtype_out == LI_BF16,
                    "linear (tcgen05 gemv): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
-        return launch_bt<bf16, kEpiSwiglu>(a, w, bias, out, M, N, K, stream, rs);
+        return epilogue == LI_EPILOGUE_GLU_CLAMPED ? launch_bt<bf16, kEpiGluClamped>(a, w, bias, out, M, N, K, stream, rs)
+                                                   : launch_bt<bf16, kEpiSwiglu>(a, w, bias, out, M, N, K, stream, rs);
     }
     if (dtype_out == LI_BF16) return launch_bt<bf16, kEpiNone>(a, w, bias, out, M, N, K, stream, rs);
     if (dtype_out == LI_F32) return launch_bt<float, kEpiNone>(a, w, bias, out, M, N, K, stream, rs);
