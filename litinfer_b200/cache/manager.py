@@ -11,7 +11,8 @@ LitInfer has one pool, free list and block table per layer
 
 Pages are allocated when a request grows (``extend``), given back when it ends
 (``release``) and, in a group with a window, as soon as every key on them lies
-behind the window of all further queries (``commit``).  The extra last page of
+behind the window of all further queries (``commit``); the pages that hold the
+first ``keep_first`` keys of such a group stay.  The extra last page of
 each tensor is a sink for padded tokens of captured decode batches; it is
 never handed out.
 
@@ -122,6 +123,9 @@ class CacheManager:
         self._h = self._lib.li_cm_create(len(self.groups), windows, self.num_pages, self.page_size, self.max_requests)
         if not self._h:
             raise PoolError("the host runtime could not create the cache manager")
+        for gid, g in enumerate(self.groups):
+            if g.key.window and g.key.keep_first:          # the pages of the first keys never go back behind the window
+                native.check(self._lib.li_cm_keep_first(self._h, gid, int(g.key.keep_first)))
         self.slots = PoolView(self, -1, self.max_requests)
         for gid, g in enumerate(self.groups):
             g.pool = PoolView(self, gid, self.num_pages)

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "li_pool_check": (I, [P]),
     "li_cm_create": (P, [I, IP, I, I, I]),
     "li_cm_destroy": (None, [P]),
+    "li_cm_keep_first": (I, [P, I, I]),
     "li_cm_num_free": (I, [P, I]),
     "li_cm_owner": (I, [P, I, I]),
     "li_cm_pool_check": (I, [P, I]),

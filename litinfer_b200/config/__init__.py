@@ -1,4 +1,5 @@
 from .filasun import FilasunConfig
+from .gorulorn import GorulornConfig
 from .qwen2 import ConfigError, Qwen2Config
 from .registry import (
     config_class_for,
@@ -14,6 +15,7 @@ __all__ = [
     "BlockSpec",
     "ConfigError",
     "FilasunConfig",
+    "GorulornConfig",
     "ModelSpec",
     "PartSpec",
     "Qwen2Config",

@@ -14,6 +14,7 @@ from pathlib import Path
 from typing import Any, Dict, Mapping, Type
 
 from .filasun import FilasunConfig
+from .gorulorn import GorulornConfig
 from .qwen2 import ConfigError, Qwen2Config
 from .spec import ModelSpec
 
@@ -63,3 +64,4 @@ def model_spec_from_dir(model_dir) -> ModelSpec:
 
 register_architecture(Qwen2Config.ARCHITECTURE, Qwen2Config)
 register_architecture(FilasunConfig.ARCHITECTURE, FilasunConfig)
+register_architecture(GorulornConfig.ARCHITECTURE, GorulornConfig)

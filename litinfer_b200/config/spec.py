@@ -98,10 +98,12 @@ class BlockSpec:
 class ScheduleEntry:
     """Run block ``block``.  ``cache_from`` None: this entry owns a cache (or
     state); otherwise it reads what schedule entry ``cache_from`` wrote in
-    this step and writes nothing."""
+    this step and writes nothing.  ``add``: (name of a table in ``ModelSpec.stream_tables``, row): that row is added to the
+    residual stream right before the block runs (a vector per pass of a span of layers that runs several times)."""
 
     block: int
     cache_from: Optional[int] = None
+    add: Optional[Tuple[str, int]] = None
 
 
 @dataclass(frozen=True)
@@ -129,6 +131,8 @@ class ModelSpec:
     # sum at the end; every block then is of an arrangement that takes them (also for 1, where those arrangements still
     # weigh what they read and write).  None: the plain single stream
     streams: Optional[int] = None
+    # tables of vectors that schedule entries add to the residual stream (``ScheduleEntry.add``): tensor name -> rows
+    stream_tables: Mapping[str, int] = field(default_factory=dict)
     # other names under which a declared tensor may be stored: declared name -> names tried after it
     aliases: Mapping[str, Tuple[str, ...]] = field(default_factory=dict)
 
@@ -146,6 +150,10 @@ def validate_schedule(spec: ModelSpec) -> None:
     for i, e in enumerate(spec.schedule):
         if not 0 <= e.block < len(spec.blocks):
             raise ValueError(f"schedule entry {i} names block {e.block}, the model has {len(spec.blocks)}")
+        if e.add is not None:
+            name, row = e.add
+            if name not in spec.stream_tables or not 0 <= int(row) < int(spec.stream_tables[name]):
+                raise ValueError(f"schedule entry {i} adds row {row} of '{name}', which the model's stream tables do not have")
         if e.cache_from is not None:
             if not 0 <= e.cache_from < i:
                 raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_from}, which does not run before it")

@@ -16,7 +16,7 @@
 int li_attention_generic(const void* qkv, void* out, const void* kcache, const void* vcache, int dtype, const int* block_table,
                          int max_blocks, const int* seq_of_token, const int* positions, int T, int nh, int nkv, int dh,
                          int page_size, int num_pages, float scale, int window, float softcap, const float* slopes, const void* gate,
-                         cudaStream_t stream);
+                         int keep_first, const float* sinks, cudaStream_t stream);
 bool li_attention_decode_accepts(int nh, int nkv, int dh, int page_size);
 int li_attention_decode(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                         const int* ctx_lens, const int* old_lens, const int* q_start, int S, int nh, int nkv, int dh, int page_size, int num_pages,
@@ -80,10 +80,14 @@ LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache,
                                  const int* seq_of_token, const int* positions, int T, int S, int nh, int nkv, int dh,
                                  int page_size, int num_pages, float scale, int window, int max_q_len, int max_ctx_len,
                                  const int* old_lens, int singles, const int* units, int slots_portions, int slots_all,
-                                 float softcap, const float* slopes, const void* gate, cudaStream_t stream) {
+                                 float softcap, const float* slopes, const void* gate, int keep_first, const float* sinks, cudaStream_t stream) {
     if (int rc = validate(T, S, nh, nkv, dh, page_size, window)) return rc;
     if (T == 0) return 0;
-    if (dtype == LI_BF16) {
+    LI_REQUIRE(keep_first >= 0, "attention: bad keep_first %d", keep_first);
+    if (window <= 0) keep_first = 0;                    // without a window every key is seen anyway
+    // kept first keys and sinks: the general kernel has them; the tensor-core kernels do not
+    const bool plain = keep_first == 0 && sinks == nullptr;
+    if (dtype == LI_BF16 && plain) {
         if (max_q_len == 1 && T == S && li_attention_decode_accepts(nh, nkv, dh, page_size))
             return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, nullptr, S, nh, nkv, dh, page_size,
                                        num_pages, scale, window, max_ctx_len, S, softcap, slopes, gate, stream);
@@ -94,7 +98,7 @@ LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache,
         if (rc || done) return rc;
     }
     return li_attention_generic(qkv, out, kcache, vcache, dtype, block_table, max_blocks, seq_of_token, positions, T, nh, nkv, dh,
-                                page_size, num_pages, scale, window, softcap, slopes, gate, stream);
+                                page_size, num_pages, scale, window, softcap, slopes, gate, keep_first, sinks, stream);
 }
 
 // old_lens (may be null): how many keys of each sequence were in the cache before this step.  Null means all but the
@@ -108,12 +112,14 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
                                       const int* seq_of_token, const int* positions, int T, int S, int nh, int nkv, int dh,
                                       int page_size, int num_pages, float scale, int window, int max_q_len, int max_ctx_len,
                                       const int* old_lens, int singles, const int* units, int slots_portions, int slots_all,
-                                      float softcap, const float* slopes, const void* gate, cudaStream_t stream) {
+                                      float softcap, const float* slopes, const void* gate, int keep_first, const float* sinks, cudaStream_t stream) {
     if (int rc = validate(T, S, nh, nkv, dh, page_size, window)) return rc;
     if (T == 0) return 0;
+    if (window <= 0) keep_first = 0;
     if (which == 0)
         return li_attention_generic(qkv, out, kcache, vcache, dtype, block_table, max_blocks, seq_of_token, positions, T, nh, nkv,
-                                    dh, page_size, num_pages, scale, window, softcap, slopes, gate, stream);
+                                    dh, page_size, num_pages, scale, window, softcap, slopes, gate, keep_first, sinks, stream);
+    LI_REQUIRE(keep_first == 0 && sinks == nullptr, "attention: implementation %d takes no kept first keys and no sinks", which);
     LI_REQUIRE(which != 3 || (softcap <= 0.0f && slopes == nullptr && gate == nullptr), "attention: the tcgen05 kernel takes no cap, slopes or gate");
     LI_REQUIRE(dtype == LI_BF16, "attention: implementation %d takes bfloat16 only", which);
     if (which == 1) {

@@ -21,6 +21,9 @@
 //   softcap > 0:  s <- softcap * tanh(s / softcap) after the scale;
 //   slopes [nh]:  s <- s - slopes[h] * (p - key), a penalty linear in the distance;
 //   gate [T, nh]: the head's output is multiplied by 1 / (1 + exp(-gate[t, h])).
+// Optional changes of what is seen and of the softmax's denominator:
+//   keep_first > 0 (with a window): keys 0 .. keep_first - 1 stay visible behind the window, at their own positions;
+//   sinks [nh]:   exp(sinks[h]) joins the denominator of head h once; it has no key and no value and is not scaled.
 #include "common.cuh"
 
 namespace {
@@ -33,7 +36,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_of_token,
                          const int* __restrict__ positions, int total, int nh, int nkv, int dh, int page_size, int num_pages,
-                         float scale, int window, float softcap, const float* __restrict__ slopes, const T* __restrict__ gate) {
+                         float scale, int window, float softcap, const float* __restrict__ slopes, const T* __restrict__ gate,
+                         int keep_first, const float* __restrict__ sinks) {
     const int warp = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (warp >= total) return;
@@ -56,7 +60,10 @@ attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, const T
     float m = -INFINITY, l = 0.0f;
     const float slope = slopes ? slopes[h] : 0.0f;
     const int* bt = block_table + (size_t)s * max_blocks;
-    for (int key = lo; key <= p; ++key) {
+    // the kept first keys that lie behind the window come first, then the window: ascending order either way
+    const int kept = keep_first < lo ? keep_first : lo;
+    for (int key = kept > 0 ? 0 : lo; key <= p; ++key) {
+        if (key == kept && key < lo) key = lo;
         const int lb = key / page_size;
         int page = bt[lb];
         if (page < 0 || page >= num_pages) page = 0;      // host-validated; keep the read inside the cache
@@ -84,6 +91,14 @@ attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, const T
         m = mn;
     }
     T* o = out + (size_t)t * nh * dh + h * dh;
+    if (sinks) {
+        const float sk = sinks[h];
+        const float mn = fmaxf(m, sk);
+        const float alpha = expf(m - mn);
+        l = l * alpha + expf(sk - mn);
+#pragma unroll
+        for (int i = 0; i < kMaxPerLane; ++i) acc[i] *= alpha;
+    }
     float inv = l > 0.0f ? 1.0f / l : 0.0f;
     if (gate) inv *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * nh + h])));
 #pragma unroll
@@ -98,7 +113,7 @@ attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, const T
 int li_attention_generic(const void* qkv, void* out, const void* kcache, const void* vcache, int dtype, const int* block_table,
                          int max_blocks, const int* seq_of_token, const int* positions, int T, int nh, int nkv, int dh,
                          int page_size, int num_pages, float scale, int window, float softcap, const float* slopes, const void* gate,
-                         cudaStream_t stream) {
+                         int keep_first, const float* sinks, cudaStream_t stream) {
     LI_REQUIRE(dh <= 32 * kMaxPerLane, "attention: head_dim %d is larger than %d", dh, 32 * kMaxPerLane);
     const long long total = (long long)T * nh;
     LI_REQUIRE(total < (1LL << 31), "attention: too many (token, head) pairs");
@@ -106,11 +121,11 @@ int li_attention_generic(const void* qkv, void* out, const void* kcache, const v
     if (dtype == LI_F32)
         attention_generic_kernel<float><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
             (const float*)qkv, (float*)out, (const float*)kcache, (const float*)vcache, block_table, max_blocks, seq_of_token, positions,
-            (int)total, nh, nkv, dh, page_size, num_pages, scale, window, softcap, slopes, (const float*)gate);
+            (int)total, nh, nkv, dh, page_size, num_pages, scale, window, softcap, slopes, (const float*)gate, keep_first, sinks);
     else if (dtype == LI_BF16)
         attention_generic_kernel<bf16><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
             (const bf16*)qkv, (bf16*)out, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks, seq_of_token, positions,
-            (int)total, nh, nkv, dh, page_size, num_pages, scale, window, softcap, slopes, (const bf16*)gate);
+            (int)total, nh, nkv, dh, page_size, num_pages, scale, window, softcap, slopes, (const bf16*)gate, keep_first, sinks);
     else
         return li_fail("attention: unknown dtype %d", dtype);
     return li_check_launch("attention (generic)");

@@ -43,6 +43,10 @@ void* li_cm_create(int groups, const int* windows, int num_pages, int page_size,
 
 void li_cm_destroy(void* h);
 
+/* The first `keys` keys of every request stay readable in a windowed group: their pages never go back behind the window.
+ * To be set before any request is admitted. */
+int li_cm_keep_first(void* h, int group, int keys);
+
 /* Free ids of a pool; which: -1 the state slots, else a group's pages. */
 int li_cm_num_free(void* h, int which);
 

@@ -52,6 +52,16 @@ LI_HOST_EXPORT void* li_cm_create(int groups, const int* windows, int num_pages,
 }
 LI_HOST_EXPORT void li_cm_destroy(void* h) { delete static_cast<Manager*>(h); }
 
+// The first `keys` keys of every request stay readable in a windowed group: their pages never go back behind the window.
+// To be set before any request is admitted.
+LI_HOST_EXPORT int li_cm_keep_first(void* h, int group, int keys) {
+    Manager* m = static_cast<Manager*>(h);
+    if (group < 0 || group >= (int)m->pools.size() || keys < 0) return fail(LI_HOST_VALUE, "keep_first: group %d, %d keys", group, keys);
+    if (!m->live.empty()) return fail(LI_HOST_POOL, "keep_first: requests are live");
+    m->keeps[(size_t)group] = keys;
+    return LI_HOST_OK;
+}
+
 // which: -1 the state slots, else a group's pages
 static Pool* pool_of(Manager* m, int which) {
     if (which < 0) return &m->slots;
@@ -79,6 +89,7 @@ int li_host::cm_admit(Manager* m, int id, int* slot) {
     r.tables.resize(m->pools.size());
     r.sent.assign(m->pools.size(), 0);
     r.trash_sent.assign(m->pools.size(), 0);
+    for (size_t g = 0; g < m->pools.size(); ++g) r.trash_sent[g] = m->kept_pages((int)g);      // pages go back from there on
     m->live.emplace(id, std::move(r));
     return LI_HOST_OK;
 }
@@ -123,7 +134,7 @@ LI_HOST_EXPORT int li_cm_commit(void* h, int id, int new_length) {
         if (m->windows[g] <= 0) continue;
         std::vector<int>& t = r->tables[g];
         const int upto = std::min(m->first_needed_page((int)g, new_length), (int)t.size());
-        for (int lp = 0; lp < upto; ++lp)
+        for (int lp = m->kept_pages((int)g); lp < upto; ++lp)
             if (t[(size_t)lp] != kReleased) {
                 if (int rc = m->pools[g].release(t[(size_t)lp], id)) return rc;
                 t[(size_t)lp] = kReleased;

@@ -77,12 +77,13 @@ struct Request {
 struct Manager {
     int page_size, num_pages, max_requests;
     std::vector<int> windows;                      // per group: keys a query still reads, 0 = all of them
+    std::vector<int> keeps;                        // per group: the first keys of a request that every later query still reads
     std::vector<Pool> pools;
     Pool slots;
     std::unordered_map<int, Request> live;
 
     Manager(int groups, const int* win, int pages, int page, int requests)
-        : page_size(page), num_pages(pages), max_requests(requests), windows(win, win + groups), slots(requests, "state slot") {
+        : page_size(page), num_pages(pages), max_requests(requests), windows(win, win + groups), keeps((size_t)groups, 0), slots(requests, "state slot") {
         for (int g = 0; g < groups; ++g) pools.emplace_back(pages, "page");
     }
     Request* find(int id) {
@@ -90,6 +91,8 @@ struct Manager {
         return it == live.end() ? nullptr : &it->second;
     }
     int blocks(int tokens) const { return (tokens + page_size - 1) / page_size; }
+    // logical pages at the start of a request that a window never gives back (they hold the kept first keys)
+    int kept_pages(int g) const { return blocks(keeps[(size_t)g]); }
     // first logical page that a query at a position >= length can still read
     int first_needed_page(int g, int length) const {
         if (windows[(size_t)g] <= 0) return 0;

@@ -38,12 +38,14 @@ int li_table_gather(int* resident, int rows, int cols, const int* updates, int u
  * two unused words, then per entry: sequence, tile of 128 tokens, part | parts << 8, unused), with the number of entries
  * to launch when the single tokens go to the decode kernel and when they do not.  softcap > 0: scores become
  * softcap * tanh(score / softcap); slopes [nh] (may be NULL): slopes[h] * (p - key) is taken off the score of head h;
- * gate [T, nh] in the run dtype (may be NULL): head h's output is multiplied by 1 / (1 + exp(-gate[t, h])). */
+ * gate [T, nh] in the run dtype (may be NULL): head h's output is multiplied by 1 / (1 + exp(-gate[t, h])).
+ * keep_first > 0 (with a window): keys 0 .. keep_first - 1 stay visible behind the window; sinks [nh] (may be NULL):
+ * exp(sinks[h]) joins the softmax's denominator of head h once, with no key and no value. */
 int li_paged_attention(const void* qkv, void* out, const void* kcache, const void* vcache, int dtype, const int*
     block_table, int max_blocks, const int* q_start, const int* ctx_lens, const int* seq_of_token, const int*
     positions, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window, int
     max_q_len, int max_ctx_len, const int* old_lens, int singles, const int* units, int slots_portions, int slots_all,
-    float softcap, const float* slopes, const void* gate, cudaStream_t stream);
+    float softcap, const float* slopes, const void* gate, int keep_first, const float* sinks, cudaStream_t stream);
 
 /* The same through one implementation: 0 general, 1 decode, 2 mma.sync tiles, 3 tcgen05 tiles (tests and
  * measurements). */
@@ -51,7 +53,7 @@ int li_paged_attention_with(int which, const void* qkv, void* out, const void* k
     const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens, const int* seq_of_token, const
     int* positions, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window, int
     max_q_len, int max_ctx_len, const int* old_lens, int singles, const int* units, int slots_portions, int slots_all,
-    float softcap, const float* slopes, const void* gate, cudaStream_t stream);
+    float softcap, const float* slopes, const void* gate, int keep_first, const float* sinks, cudaStream_t stream);
 
 /* ---- decode_step.cu: a decode step as one persistent kernel (decode_step.h has the structures) ---- */
 struct LiDecodeStep;
@@ -213,6 +215,50 @@ int li_linear_rope_kv(const void* a, const void* w, const float* bias, void* qkv
     const float* denom, int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T, int K, int nh, int
     nkv, int dh, int page_size, int num_pages, int write, int allow_fused, const float* ssq, int nparts, int width,
     float eps, const float* cos_sin, cudaStream_t stream);
+
+/* ---- norm_pair.cu: norms before and after a sublayer in one pass over the residual stream ---- */
+/* Per row: x += post(y) (post: a norm of y [R, H] with the weight w_post; NULL: x += y; y NULL: nothing is added), then
+ * out = next(x) if w_next is given.  A norm is centered (mean taken off, variance as the mean of squared deviations:
+ * layer norm without bias) or not (RMS norm).  rows (may be NULL; only without y): out[r] = next(x[rows[r]]). */
+int li_norm_add_norm(float* x, const void* y, int dtype, const float* w_post, int post_centered, float eps_post, const float* w_next,
+    int next_centered, float eps_next, void* out, const int* rows, int R, int n_src, int H, cudaStream_t stream);
+
+/* x[t] += row for every token. */
+int li_add_row(float* x, const float* row, int T, int H, cudaStream_t stream);
+
+/* RMS norm of the columns col .. col + n - 1 of in [T, ld_in] (mean of squares over `width` elements), written to out
+ * [T, ld_out] at col_a and, if col_b >= 0, at col_b too. */
+int li_rmsnorm_cols(const void* in, int dtype, int ld_in, int col, int n, int width, const float* w, float eps, void* out, int ld_out,
+    int col_a, int col_b, int T, cudaStream_t stream);
+
+/* ---- qkv_post.cu: between the q|k|v product and attention ---- */
+/* A short causal convolution per channel (conv_w [(nh + 2 nkv) dh, taps]; inputs before a portion from state [slots,
+ * state_stride] at state_off), an RMS norm per query and key head (q_norm, k_norm [dh], mean over norm_width elements),
+ * the rotation of the first rotary_dim elements, q to out, k and v into the paged cache.  Every step is optional. */
+int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* conv_w, int taps, const float* state,
+    long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
+    const float* q_norm, const float* k_norm, float eps, int norm_width, const int* positions, const float* denom,
+    int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T, int nh, int nkv, int dh,
+    int page_size, int num_pages, int write, cudaStream_t stream);
+
+/* ---- grouped.cu: products in groups, routing of a mixture of experts ---- */
+/* out_g = a_g w_g^T, w [G, N, K].  row_offsets [G + 1] (device): group g owns those rows of a [M, lda] and out [M, ldc].
+ * row_offsets NULL: every group takes all M rows, inputs at column g * a_gcol, outputs at column g * c_gcol. */
+int li_grouped_linear(const void* a, int lda, int a_gcol, const void* w, void* out, int ldc, int c_gcol, const int* row_offsets, int dtype,
+    int M, int N, int K, int G, cudaStream_t stream);
+
+/* ids, weights [T, top]: the experts with the largest sigmoid(logits [T, E]) and those scores. */
+int li_moe_route(const float* logits, int T, int E, int top, int* ids, float* weights, cudaStream_t stream);
+
+/* Stable sort of n (token, choice) pairs by expert: offsets [E + 1], pair_at [n] (pair at a sorted place), place_of [n]. */
+int li_moe_sort(const int* ids, int n, int E, int* offsets, int* pair_at, int* place_of, cudaStream_t stream);
+
+/* out [n, H]: row r is h[pair_at[r] / top], times weights[pair_at[r]] if weights is given. */
+int li_moe_gather(const void* h, int dtype, const int* pair_at, const float* weights, int n, int top, int H, void* out, cudaStream_t stream);
+
+/* y [T, H]: y[t] = sum_k rows[place_of[t * top + k]] (times weights[t * top + k] if weights is given). */
+int li_moe_combine(const void* rows, int dtype, const int* place_of, const float* weights, int T, int top, int H, void* y,
+    cudaStream_t stream);
 
 /* ---- sampling.cu ---- */
 /* out[r] = the first maximum of logits[r]. */

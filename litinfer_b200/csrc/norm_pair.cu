@@ -1,0 +1,150 @@
+// Norms around a sublayer ("sandwich" arrangement) as one pass over the residual stream, and two small
+// helpers of the same family.
+//
+//   li_norm_add_norm: per token row
+//       x += post(y)          post: a norm of the sublayer's output y with its own weight (or none: x += y; or no y at all)
+//       out = next(x)         next: the norm that feeds the following sublayer (optional)
+//     where a norm is  (v - mean) / sqrt(var + eps) * w  (centered: layer norm without bias, var the mean of the squared
+//     deviations) or  v / sqrt(mean(v^2) + eps) * w  (not centered: RMS norm).  Rows may be gathered (rows[r]) when
+//     there is no y: the model's last norm on the wanted rows only.
+//   li_add_row: x[t] += table[row] for every token (a vector per pass of a looped span of layers).
+//   li_rmsnorm_cols: RMS norm of n columns of a run-dtype matrix, written to (up to) two places of another matrix.
+//
+// All sums, means and the residual stream are float; y and out are in the run dtype.  One block per row; the row is
+// read again from cache for the second moment, so that the variance is the mean of squared deviations, not a
+// difference of large sums.
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float row_stat_norm(const T* __restrict__ v, int H, int centered, float eps, float* scratch, float* mean_out) {
+    float mean = 0.0f;
+    if (centered) {
+        float s = 0.0f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) s += to_float(v[i]);
+        mean = block_sum(s, scratch) / (float)H;
+    }
+    float q = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float d = to_float(v[i]) - mean;
+        q = fmaf(d, d, q);
+    }
+    q = block_sum(q, scratch);
+    *mean_out = mean;
+    return 1.0f / sqrtf(q / (float)H + eps);
+}
+
+template <typename T>
+__global__ void norm_add_norm_kernel(float* __restrict__ x, const T* __restrict__ y, const float* __restrict__ w_post, int post_centered,
+                                     float eps_post, const float* __restrict__ w_next, int next_centered, float eps_next,
+                                     T* __restrict__ out, const int* __restrict__ rows, int n_src, int H) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    int src = r;
+    if (rows) {
+        src = rows[r];
+        if (src < 0 || src >= n_src) src = 0;
+    }
+    float* xr = x + (size_t)src * H;
+    if (y) {
+        const T* yr = y + (size_t)r * H;
+        if (w_post) {
+            float mean;
+            const float rinv = row_stat_norm(yr, H, post_centered, eps_post, scratch, &mean);
+            for (int i = threadIdx.x; i < H; i += blockDim.x) xr[i] += (to_float(yr[i]) - mean) * rinv * w_post[i];
+        } else {
+            for (int i = threadIdx.x; i < H; i += blockDim.x) xr[i] += to_float(yr[i]);
+        }
+        __syncthreads();                                  // the row's new values are read by other threads below
+    }
+    if (w_next) {
+        float mean;
+        const float rinv = row_stat_norm(xr, H, next_centered, eps_next, scratch, &mean);
+        T* o = out + (size_t)r * H;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<T>((xr[i] - mean) * rinv * w_next[i]);
+    }
+}
+
+__global__ void add_row_kernel(float* __restrict__ x, const float* __restrict__ row, long long n, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += row[i % H];
+}
+
+template <typename T>
+__global__ void rmsnorm_cols_kernel(const T* __restrict__ in, int ld_in, int col, int n, int width, const float* __restrict__ w, float eps,
+                                    T* __restrict__ out, int ld_out, int col_a, int col_b) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const T* v = in + (size_t)blockIdx.x * ld_in + col;
+    float q = 0.0f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float a = to_float(v[i]);
+        q = fmaf(a, a, q);
+    }
+    q = block_sum(q, scratch);
+    const float rinv = 1.0f / sqrtf(q / (float)width + eps);
+    T* o = out + (size_t)blockIdx.x * ld_out;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const T r = from_float<T>(to_float(v[i]) * rinv * w[i]);
+        o[col_a + i] = r;
+        if (col_b >= 0) o[col_b + i] = r;
+    }
+}
+
+}  // namespace
+
+// y (may be NULL): [R, H] in the run dtype; w_post (may be NULL: x += y); w_next (may be NULL: no output); rows (may
+// be NULL; only without y): out[r] = next(x[rows[r]]).  x is [n_src, H] float and is changed in place when y is given.
+LI_EXPORT int li_norm_add_norm(float* x, const void* y, int dtype, const float* w_post, int post_centered, float eps_post, const float* w_next,
+                               int next_centered, float eps_next, void* out, const int* rows, int R, int n_src, int H, cudaStream_t stream) {
+    LI_REQUIRE(R >= 0 && H > 0 && n_src >= 0, "norm_add_norm: bad sizes R=%d H=%d", R, H);
+    LI_REQUIRE(y == nullptr || rows == nullptr, "norm_add_norm: gathered rows cannot take a sublayer's output");
+    LI_REQUIRE(w_next == nullptr || out != nullptr, "norm_add_norm: a following norm needs an output");
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "norm_add_norm: unknown dtype %d", dtype);
+    if (R == 0) return 0;
+    const int threads = H >= 2048 ? 512 : H >= 512 ? 256 : 128;
+    cudaError_t e;
+    if (dtype == LI_F32)
+        e = li_launch_pdl(norm_add_norm_kernel<float>, dim3(R), dim3(threads), 0, stream, x, (const float*)y, w_post, post_centered, eps_post,
+                          w_next, next_centered, eps_next, (float*)out, rows, n_src, H);
+    else
+        e = li_launch_pdl(norm_add_norm_kernel<bf16>, dim3(R), dim3(threads), 0, stream, x, (const bf16*)y, w_post, post_centered, eps_post,
+                          w_next, next_centered, eps_next, (bf16*)out, rows, n_src, H);
+    if (e != cudaSuccess) return li_fail("norm_add_norm: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("norm_add_norm");
+}
+
+LI_EXPORT int li_add_row(float* x, const float* row, int T, int H, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && H > 0, "add_row: bad sizes");
+    if (T == 0) return 0;
+    const long long n = (long long)T * H;
+    const cudaError_t e = li_launch_pdl(add_row_kernel, dim3((unsigned)ceil_div_ll(n, 256)), dim3(256), 0, stream, x, row, n, H);
+    if (e != cudaSuccess) return li_fail("add_row: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("add_row");
+}
+
+// in [T, ld_in]: columns col .. col + n - 1 are normalised (the mean of squares taken over `width` elements: n, or fewer
+// when the last columns are padding that holds zeros) and written to out [T, ld_out] at col_a and, if col_b >= 0, at col_b.
+LI_EXPORT int li_rmsnorm_cols(const void* in, int dtype, int ld_in, int col, int n, int width, const float* w, float eps, void* out, int ld_out,
+                              int col_a, int col_b, int T, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && n > 0 && width > 0 && width <= n && col >= 0 && col + n <= ld_in, "rmsnorm_cols: bad columns");
+    LI_REQUIRE(col_a >= 0 && col_a + n <= ld_out && col_b + n <= ld_out, "rmsnorm_cols: bad output columns");
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "rmsnorm_cols: unknown dtype %d", dtype);
+    if (T == 0) return 0;
+    const int threads = n >= 512 ? 256 : 128;
+    cudaError_t e;
+    if (dtype == LI_F32)
+        e = li_launch_pdl(rmsnorm_cols_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)in, ld_in, col, n, width, w, eps, (float*)out,
+                          ld_out, col_a, col_b);
+    else
+        e = li_launch_pdl(rmsnorm_cols_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)in, ld_in, col, n, width, w, eps, (bf16*)out,
+                          ld_out, col_a, col_b);
+    if (e != cudaSuccess) return li_fail("rmsnorm_cols: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("rmsnorm_cols");
+}

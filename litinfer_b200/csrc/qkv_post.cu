@@ -1,0 +1,174 @@
+// What may stand between the q|k|v product and attention, as one kernel:
+//
+//   1. a short causal convolution over time on every channel of q, k and v (no bias, no activation):
+//        u'_t[c] = sum_j w[c][j] u_(t - taps + 1 + j)[c],
+//      inputs before a sequence's portion come from the request's state (the last taps - 1 projected rows, oldest
+//      first), zeros before the sequence's start (a cleared state);
+//   2. an RMS norm per head on queries and keys, with a weight of head size shared by the heads;
+//   3. the rotation of the first rotary_dim elements of each query and key head (pair j with j + rotary_dim / 2,
+//      angle float(pos) / denom[j]);
+//   4. q written to `out` (the q columns of a [T, (nh + 2 nkv) dh] row), k and v into the paged cache (values transposed).
+//
+// Each step is optional (taps <= 1, null norm weights, rotary_dim 0).  One warp per (token, head of q|k|v); the head's
+// elements stay in registers, the rotation's partners meet through shared memory.  Convolution, norm and angles are
+// computed in float from run-dtype inputs and rounded once.  The state itself is moved on by li_conv_state_shift.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kPerLane = 16;        // head_dim <= 512
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const float* __restrict__ conv_w, int taps,
+                         const float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ q_start,
+                         const int* __restrict__ seq_of_token, const int* __restrict__ slots, const float* __restrict__ q_norm,
+                         const float* __restrict__ k_norm, float eps, int norm_width, const int* __restrict__ positions,
+                         const float* __restrict__ denom, int rotary_dim, const int* __restrict__ slot_mapping, T* __restrict__ kcache,
+                         T* __restrict__ vcache, int total, int nh, int nkv, int dh, int page_size, int num_pages, int write) {
+    extern __shared__ float smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * kWarps + warp_in_block;
+    if (unit >= total) return;
+    const int heads = nh + 2 * nkv;
+    const int t = unit / heads, head = unit - t * heads;
+    const int N = heads * dh;
+    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+    if (!is_q && !write) return;
+    const int c0 = head * dh;
+    const int per = (dh + 31) >> 5;
+    float v[kPerLane];
+    // 1. the convolution (or the plain value)
+    if (taps > 1) {
+        const int s = seq_of_token[t];
+        const int q0 = q_start[s];
+        const int li = t - q0;
+        const float* st = state + (size_t)slots[s] * state_stride + state_off;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+            const int d = lane + 32 * i;
+            float acc = 0.0f;
+            if (i < per && d < dh) {
+                const int c = c0 + d;
+                for (int j = 0; j < taps; ++j) {
+                    const int src = li - (taps - 1) + j;
+                    const float u = src >= 0 ? to_float(proj[(size_t)(q0 + src) * N + c]) : st[(size_t)(taps - 1 + src) * N + c];
+                    acc = fmaf(conv_w[(size_t)c * taps + j], u, acc);
+                }
+            }
+            v[i] = acc;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+            const int d = lane + 32 * i;
+            v[i] = (i < per && d < dh) ? to_float(proj[(size_t)t * N + c0 + d]) : 0.0f;
+        }
+    }
+    // 2. the norm of a query or key head
+    const float* nw = is_q ? q_norm : (is_k ? k_norm : nullptr);
+    if (nw) {
+        float q = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) q = fmaf(v[i], v[i], q);
+        q = warp_sum(q);
+        const float rinv = 1.0f / sqrtf(q / (float)norm_width + eps);
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (i < per && d < dh) v[i] = v[i] * rinv * nw[d];
+        }
+    }
+    // 3. the rotation
+    if (rotary_dim > 0 && (is_q || is_k)) {
+        float* sh = smem + (size_t)warp_in_block * dh;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (i < per && d < dh) sh[d] = v[i];
+        }
+        __syncwarp();
+        const int half = rotary_dim >> 1;
+        const float pos = (float)positions[t];
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (i < per && d < rotary_dim) {
+                const int j = d < half ? d : d - half;
+                float sn, cs;
+                sincosf(pos / denom[j], &sn, &cs);
+                const float a = sh[j], b = sh[j + half];
+                v[i] = d < half ? a * cs - b * sn : b * cs + a * sn;
+            }
+        }
+    }
+    // 4. where it goes
+    if (is_q) {
+        T* o = out + (size_t)t * N + c0;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (i < per && d < dh) o[d] = from_float<T>(v[i]);
+        }
+        return;
+    }
+    const int slot = slot_mapping[t];
+    const int page = slot / page_size, off = slot - page * page_size;
+    if (slot < 0 || page >= num_pages) return;              // validated on the host; never write outside the cache
+    if (is_k) {
+        T* dst = kcache + (((size_t)page * nkv + (head - nh)) * page_size + off) * dh;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (i < per && d < dh) dst[d] = from_float<T>(v[i]);
+        }
+    } else {
+        T* dst = vcache + ((size_t)page * nkv + (head - nh - nkv)) * dh * page_size + off;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (i < per && d < dh) dst[(size_t)d * page_size] = from_float<T>(v[i]);
+        }
+    }
+}
+
+}  // namespace
+
+// proj, out: [T, (nh + 2 nkv) dh] in the run dtype (out may not be proj when taps > 1: tokens read their neighbours' rows).
+// conv_w [(nh + 2 nkv) dh, taps] float (NULL or taps <= 1: no convolution); state [slots, state_stride] float with the
+// convolution's rows at state_off; q_norm, k_norm [dh] float (NULL: no norm), the mean of squares over norm_width
+// elements (dh, or fewer when heads are padded with zeros); rotary_dim 0: no rotation.  write 0: only q is made.
+LI_EXPORT int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* conv_w, int taps, const float* state,
+                                   long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
+                                   const float* q_norm, const float* k_norm, float eps, int norm_width, const int* positions, const float* denom,
+                                   int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T, int nh, int nkv, int dh,
+                                   int page_size, int num_pages, int write, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && dh > 0 && page_size > 0, "conv_norm_rope_kv: bad sizes");
+    LI_REQUIRE(dh <= 32 * kPerLane, "conv_norm_rope_kv: head_dim %d is larger than %d", dh, 32 * kPerLane);
+    LI_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= dh, "conv_norm_rope_kv: rotary_dim %d must be even and at most head_dim %d",
+               rotary_dim, dh);
+    LI_REQUIRE(rotary_dim == 0 || denom != nullptr, "conv_norm_rope_kv: rotary_dim %d without denominators", rotary_dim);
+    LI_REQUIRE(taps <= 1 || (conv_w != nullptr && state != nullptr && proj != out), "conv_norm_rope_kv: a convolution needs weights, a state and an output of its own");
+    LI_REQUIRE((q_norm == nullptr) == (k_norm == nullptr), "conv_norm_rope_kv: queries and keys are normalised together or not at all");
+    LI_REQUIRE(norm_width > 0 && norm_width <= dh, "conv_norm_rope_kv: bad norm width %d", norm_width);
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "conv_norm_rope_kv: unknown dtype %d", dtype);
+    if (T == 0) return 0;
+    const long long total = (long long)T * (nh + 2 * nkv);
+    LI_REQUIRE(total < (1LL << 31), "conv_norm_rope_kv: too many (token, head) pairs");
+    const dim3 grid((unsigned)ceil_div_ll(total, kWarps));
+    const size_t smem = (size_t)kWarps * dh * sizeof(float);
+    cudaError_t e;
+    if (dtype == LI_F32)
+        e = li_launch_pdl(conv_norm_rope_kv_kernel<float>, grid, dim3(kWarps * 32), smem, stream, (const float*)proj, (float*)out, conv_w, taps,
+                          state, state_stride, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, positions, denom,
+                          rotary_dim, slot_mapping, (float*)kcache, (float*)vcache, (int)total, nh, nkv, dh, page_size, num_pages, write);
+    else
+        e = li_launch_pdl(conv_norm_rope_kv_kernel<bf16>, grid, dim3(kWarps * 32), smem, stream, (const bf16*)proj, (bf16*)out, conv_w, taps,
+                          state, state_stride, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, positions, denom,
+                          rotary_dim, slot_mapping, (bf16*)kcache, (bf16*)vcache, (int)total, nh, nkv, dh, page_size, num_pages, write);
+    if (e != cudaSuccess) return li_fail("conv_norm_rope_kv: launch failed: %s", cudaGetErrorString(e));
+    return li_check_launch("conv_norm_rope_kv");
+}

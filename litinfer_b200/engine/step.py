@@ -81,7 +81,8 @@ class ModelRunner:
         self._may_split = not any(has_fixed_state(r) for r in model.cache_requirements())
 
         def mixers_with_state(part):
-            if isinstance(part, Mixer) and isinstance(part.cache_requirement(), FixedState):          # (a mixer of mixers: its parts answer)
+            # (a mixer of mixers: its parts answer; a mixer that keeps pages and a state answers for itself)
+            if isinstance(part, Mixer) and has_fixed_state(part.cache_requirement()) and not any(isinstance(c, Mixer) for c in part.parts()):
                 yield part
             for child in part.parts():
                 yield from mixers_with_state(child)

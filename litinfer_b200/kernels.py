@@ -420,7 +420,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                     max_q_len: int, max_ctx_len: int, implementation: Optional[str] = None,
                     old_lens: Optional[torch.Tensor] = None, singles: int = 0,
                     units: Optional[torch.Tensor] = None, unit_slots: Tuple[int, int] = (0, 0),
-                    softcap: float = 0.0, slopes: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+                    softcap: float = 0.0, slopes: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                    keep_first: int = 0, sinks: Optional[torch.Tensor] = None) -> None:
     """Causal grouped-query attention of the step's tokens over the paged cache.
 
     Queries are the first ``num_heads * head_dim`` columns of ``qkv`` (already
@@ -436,7 +437,10 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     ``unit_slots`` = how many entries to launch when the single tokens are the decode kernel's, and when not.
     ``softcap`` > 0: a score s becomes ``softcap * tanh(s / softcap)`` (after the scale).  ``slopes`` (float32
     ``[num_heads]``): ``slopes[h] * (p - key)`` is taken off the scores of head h, a penalty linear in the distance.
-    ``gate`` (run dtype ``[T, num_heads]``): head h's output is multiplied by ``sigmoid(gate[t, h])``."""
+    ``gate`` (run dtype ``[T, num_heads]``): head h's output is multiplied by ``sigmoid(gate[t, h])``.
+    ``keep_first`` (with a window): the keys ``0 .. keep_first - 1`` stay visible behind the window, at their own positions.
+    ``sinks`` (float32 ``[num_heads]``): ``exp(sinks[h])`` joins the denominator of head h's softmax once; it has no key
+    and no value and is not scaled."""
     T = qkv.shape[0]
     S = ctx_lens.shape[0]
     _need(qkv, "qkv", None, (T, (num_heads + 2 * num_kv_heads) * head_dim))
@@ -465,7 +469,9 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
             _p(q_start), _p(ctx_lens), _p(seq_of_token), _p(positions), _i(T), _i(S),
             _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages), _f(scale),
             _i(0 if window is None else int(window)), _i(max_q_len), _i(max_ctx_len), _p(old_lens), _i(int(singles)),
-            _p(units), _i(int(unit_slots[0])), _i(int(unit_slots[1])), _f(float(softcap or 0.0)), _p(slopes), _p(gate), _stream(out))
+            _p(units), _i(int(unit_slots[0])), _i(int(unit_slots[1])), _f(float(softcap or 0.0)), _p(slopes), _p(gate), _i(int(keep_first or 0)), _p(sinks), _stream(out))
+    if sinks is not None:
+        _need(sinks, "softmax sinks", torch.float32, (num_heads,))
     if slopes is not None:
         _need(slopes, "distance slopes", torch.float32, (num_heads,))
     if gate is not None:
@@ -736,6 +742,177 @@ def gated_rmsnorm(y32: torch.Tensor, gate: torch.Tensor, gate_col: int, weight: 
                                       _i(0 if gate_first else 1), _p(out), _i(T), _i(n), _i(groups), _stream(out)), "gated_rmsnorm")
 
 
+# --------------------------------------------------------------------------
+# norms on both sides of a sublayer, a vector per pass, norms of column ranges
+# --------------------------------------------------------------------------
+
+def norm_add_norm(x32: torch.Tensor, y: Optional[torch.Tensor], post: Optional[tuple], nxt: Optional[tuple], out: Optional[torch.Tensor],
+                  rows: Optional[torch.Tensor] = None) -> None:
+    """Per token: ``x32 += post(y)``, then ``out = nxt(x32)``.  A norm is a tuple ``(weight, centered, eps)``: centered takes
+    the mean off and divides by the root of the variance (mean of squared deviations) + eps, not centered divides by the
+    root of the mean of squares + eps; both multiply by the weight.  ``post`` None: ``x32 += y``; ``y`` None: nothing is
+    added; ``nxt`` None: no output.  ``rows`` (int32, only without ``y``): ``out[r] = nxt(x32[rows[r]])``."""
+    n_src, H = x32.shape
+    _need(x32, "residual stream", torch.float32)
+    R = n_src if rows is None else rows.shape[0]
+    if y is not None:
+        _need(y, "sublayer output", None, (n_src, H))
+        if rows is not None:
+            raise KernelError("norm_add_norm: gathered rows cannot take a sublayer's output")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    wp, cp, ep = post if post is not None else (None, False, 0.0)
+    wn, cn, en = nxt if nxt is not None else (None, False, 0.0)
+    if wp is not None:
+        _need(wp, "norm weight (after the sublayer)", torch.float32, (H,))
+    if wn is not None:
+        _need(wn, "norm weight (before the next sublayer)", torch.float32, (H,))
+        _need(out, "normalised output", y.dtype if y is not None else None, (R, H))
+    dt = _dt(y) if y is not None else _dt(out)
+    _check(library().li_norm_add_norm(_p(x32), _p(y), _i(dt), _p(wp), _i(1 if cp else 0), _f(ep), _p(wn), _i(1 if cn else 0), _f(en),
+                                      _p(out if wn is not None else None), _p(rows), _i(R), _i(n_src), _i(H), _stream(x32)), "norm_add_norm")
+
+
+def add_row(x32: torch.Tensor, row: torch.Tensor) -> None:
+    """x32[t] += row for every token (float32)."""
+    T, H = x32.shape
+    _need(x32, "residual stream", torch.float32)
+    _need(row, "row", torch.float32, (H,))
+    _check(library().li_add_row(_p(x32), _p(row), _i(T), _i(H), _stream(x32)), "add_row")
+
+
+def rmsnorm_cols(x: torch.Tensor, col: int, n: int, width: int, weight: torch.Tensor, eps: float, out: torch.Tensor, col_a: int,
+                 col_b: int = -1) -> None:
+    """RMS norm of the columns ``col .. col + n - 1`` of ``x`` (the mean of squares over ``width`` elements: fewer than n when
+    the last columns are zero padding), times ``weight`` [n]; written to ``out`` at column ``col_a`` and, if given, ``col_b``."""
+    T = x.shape[0]
+    _need(x, "norm input")
+    _need(weight, "rmsnorm weight", torch.float32, (n,))
+    _need(out, "norm output", x.dtype)
+    if out.shape[0] != T:
+        raise KernelError(f"rmsnorm_cols: {out.shape[0]} output rows for {T} tokens")
+    _check(library().li_rmsnorm_cols(_p(x), _i(_dt(x)), _i(x.shape[1]), _i(col), _i(n), _i(width), _p(weight), _f(eps), _p(out), _i(out.shape[1]),
+                                     _i(col_a), _i(col_b), _i(T), _stream(out)), "rmsnorm_cols")
+
+
+def conv_norm_rope_kv(proj: torch.Tensor, out: torch.Tensor, conv_w: Optional[torch.Tensor], state: Optional[torch.Tensor], state_off: int,
+                      q_start: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor, q_norm: Optional[torch.Tensor],
+                      k_norm: Optional[torch.Tensor], eps: float, norm_width: int, positions: torch.Tensor,
+                      denominators: Optional[torch.Tensor], rotary_dim: int, slot_mapping: torch.Tensor, k_cache: torch.Tensor,
+                      v_cache: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, write: bool = True) -> None:
+    """What stands between a q|k|v product ``proj`` [T, (heads + 2 kv_heads) head_dim] and attention: a causal convolution
+    per channel over the last ``taps`` projected rows (``conv_w`` float32 [channels, taps], the last column the token's own;
+    rows before a portion come from ``state[slot, state_off:]`` as [taps - 1, channels], oldest first; None: none), an RMS
+    norm per query and key head (``q_norm``, ``k_norm`` [head_dim], the mean over ``norm_width`` elements; None: none), the
+    rotation of the first ``rotary_dim`` elements of queries and keys; queries to the q columns of ``out``, keys and values
+    into the paged cache.  The state is not changed (:func:`conv_state_shift` moves it on)."""
+    T = proj.shape[0]
+    N = (num_heads + 2 * num_kv_heads) * head_dim
+    _need(proj, "q|k|v projection", None, (T, N))
+    _need(out, "q|k|v output", proj.dtype, (T, N))
+    taps = 1
+    if conv_w is not None:
+        _need(conv_w, "convolution weight", torch.float32)
+        if conv_w.dim() != 2 or conv_w.shape[0] != N:
+            raise KernelError(f"conv_norm_rope_kv: convolution weight of shape {tuple(conv_w.shape)} for {N} channels")
+        taps = conv_w.shape[1]
+    st, stride, off = (_p(None), _l(0), _l(0))
+    if taps > 1:
+        st, stride, off = _state_args(state, state_off)
+        if state_off + (taps - 1) * N > state.shape[1]:
+            raise KernelError("conv_norm_rope_kv: the state is too small for the convolution's inputs")
+    for t, n in ((q_norm, "query norm weight"), (k_norm, "key norm weight")):
+        if t is not None:
+            _need(t, n, torch.float32, (head_dim,))
+    _need(positions, "positions", torch.int32, (T,))
+    if rotary_dim:
+        _need(denominators, "rope denominators", torch.float32, (rotary_dim // 2,))
+    _need(slot_mapping, "slot mapping", torch.int32, (T,))
+    _need(q_start, "q_start", torch.int32)
+    _need(seq_of_token, "seq_of_token", torch.int32, (T,))
+    _need(slots, "state slots", torch.int32)
+    _need(k_cache, "key cache", proj.dtype)
+    pages, nkv, page_size, dh = k_cache.shape
+    _need(v_cache, "value cache", proj.dtype, (pages, nkv, dh, page_size))
+    if nkv != num_kv_heads or dh != head_dim:
+        raise KernelError(f"cache of {nkv} heads x {dh} does not match {num_kv_heads} x {head_dim}")
+    _check(library().li_conv_norm_rope_kv(
+        _p(proj), _p(out), _i(_dt(proj)), _p(conv_w if taps > 1 else None), _i(taps), st, stride, off, _p(q_start), _p(seq_of_token), _p(slots),
+        _p(q_norm), _p(k_norm), _f(eps), _i(int(norm_width)), _p(positions), _p(denominators if rotary_dim else None), _i(rotary_dim),
+        _p(slot_mapping), _p(k_cache), _p(v_cache), _i(T), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages),
+        _i(1 if write else 0), _stream(out)), "conv_norm_rope_kv")
+
+
+# --------------------------------------------------------------------------
+# products in groups; routing of a mixture of experts
+# --------------------------------------------------------------------------
+
+def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_offsets: Optional[torch.Tensor] = None,
+                   a_group_cols: int = 0, out_group_cols: int = 0) -> None:
+    """``weight`` [G, N, K]: a product per group.  With ``row_offsets`` (int32 [G + 1] on the device) group g owns the rows
+    ``row_offsets[g] .. row_offsets[g + 1] - 1`` of ``a`` [M, K] and ``out`` [M, N].  Without, every group takes all rows, its
+    inputs at column ``g * a_group_cols`` of ``a`` and its outputs at column ``g * out_group_cols`` of ``out`` (a map per head)."""
+    G, N, Kd = weight.shape
+    M = a.shape[0]
+    _need(a, "grouped input")
+    _need(weight, "grouped weights", a.dtype)
+    _need(out, "grouped output", a.dtype)
+    if out.shape[0] != M:
+        raise KernelError(f"grouped_linear: {out.shape[0]} output rows for {M} input rows")
+    if row_offsets is not None:
+        _need(row_offsets, "row offsets", torch.int32, (G + 1,))
+        if a.shape[1] != Kd or out.shape[1] != N or a_group_cols or out_group_cols:
+            raise KernelError(f"grouped_linear: rows in groups need a [M, {Kd}] and out [M, {N}]")
+    elif (G - 1) * a_group_cols + Kd > a.shape[1] or (G - 1) * out_group_cols + N > out.shape[1]:
+        raise KernelError("grouped_linear: the groups' columns do not fit the rows")
+    _check(library().li_grouped_linear(_p(a), _i(a.shape[1]), _i(a_group_cols), _p(weight), _p(out), _i(out.shape[1]), _i(out_group_cols),
+                                       _p(row_offsets), _i(_dt(a)), _i(M), _i(N), _i(Kd), _i(G), _stream(out)), "grouped_linear")
+
+
+def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """``ids``, ``weights`` [T, top]: per token the experts with the largest ``sigmoid(logits)`` (the lower index wins a tie)
+    and those scores."""
+    T, E = logits.shape
+    _need(logits, "router logits", torch.float32)
+    _need(ids, "expert ids", torch.int32, (T, top))
+    _need(weights, "expert weights", torch.float32, (T, top))
+    _check(library().li_moe_route(_p(logits), _i(T), _i(E), _i(top), _p(ids), _p(weights), _stream(ids)), "moe_route")
+
+
+def moe_sort(ids: torch.Tensor, experts: int, offsets: torch.Tensor, pair_at: torch.Tensor, place_of: torch.Tensor) -> None:
+    """A stable sort of the (token, choice) pairs by expert: ``offsets`` [experts + 1] (where each expert's rows start),
+    ``pair_at`` [n] (which pair stands at a sorted place), ``place_of`` [n] (the sorted place of a pair)."""
+    n = ids.numel()
+    _need(ids, "expert ids", torch.int32)
+    _need(offsets, "row offsets", torch.int32, (experts + 1,))
+    _need(pair_at, "pair at place", torch.int32, (n,))
+    _need(place_of, "place of pair", torch.int32, (n,))
+    _check(library().li_moe_sort(_p(ids), _i(n), _i(experts), _p(offsets), _p(pair_at), _p(place_of), _stream(ids)), "moe_sort")
+
+
+def moe_gather(h: torch.Tensor, pair_at: torch.Tensor, weights: Optional[torch.Tensor], top: int, out: torch.Tensor) -> None:
+    """``out[r] = h[pair_at[r] // top]``, times ``weights.flatten()[pair_at[r]]`` if given (the weight on the expert's input)."""
+    T, H = h.shape
+    n = pair_at.shape[0]
+    _need(h, "feed-forward input")
+    _need(pair_at, "pair at place", torch.int32, (T * top,))
+    if weights is not None:
+        _need(weights, "expert weights", torch.float32, (T, top))
+    _need(out, "sorted rows", h.dtype, (n, H))
+    _check(library().li_moe_gather(_p(h), _i(_dt(h)), _p(pair_at), _p(weights), _i(n), _i(top), _i(H), _p(out), _stream(out)), "moe_gather")
+
+
+def moe_combine(rows: torch.Tensor, place_of: torch.Tensor, weights: Optional[torch.Tensor], top: int, y: torch.Tensor) -> None:
+    """``y[t] = sum_k rows[place_of[t * top + k]]`` (times ``weights[t, k]`` if given), summed in float32 in the order of k."""
+    T, H = y.shape
+    _need(rows, "sorted rows", None, (T * top, H))
+    _need(place_of, "place of pair", torch.int32, (T * top,))
+    if weights is not None:
+        _need(weights, "expert weights", torch.float32, (T, top))
+    _need(y, "feed-forward output", rows.dtype)
+    _check(library().li_moe_combine(_p(rows), _i(_dt(rows)), _p(place_of), _p(weights), _i(T), _i(top), _i(H), _p(y), _stream(y)), "moe_combine")
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     """Index of the first maximum of each row."""
     R, V = logits.shape
@@ -837,7 +1014,8 @@ TRACE = _env_on("LLAISYS_TRACE")          # LitInfer's other switch (src/llaisys
 _TIMED = ("embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "linear_add_scaled", "apply_row_scale",
           "rope_kv_write", "linear_rope_kv", "rope_table", "paged_attention", "swiglu", "argmax", "sample", "gather_rows", "scale_inplace",
           "logit_cap", "glu_clamped", "weighted_sum2", "add_position_rows", "hc_expand", "hc_read_norm", "hc_update", "causal_conv_silu", "conv_state_shift",
-          "ssm_scan", "decay_scan", "gated_rmsnorm")
+          "ssm_scan", "decay_scan", "gated_rmsnorm", "norm_add_norm", "add_row", "rmsnorm_cols", "conv_norm_rope_kv", "grouped_linear", "moe_route",
+          "moe_sort", "moe_gather", "moe_combine")
 if profile.enabled:
     for _name in _TIMED:
         globals()[_name] = profile.wrap(_name, globals()[_name])

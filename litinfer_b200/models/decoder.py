@@ -53,6 +53,7 @@ class DecoderModel:
         self.final_norm = NORMS.build(spec.final_norm, spec.final_norm_prefix, self.dtype, self.device)
         self.position = (POSITIONS.build(spec.position, spec.position_prefix, self.dtype, self.device)
                          if spec.position is not None else None)
+        self.stream_tables: Dict[str, torch.Tensor] = {}      # vectors that schedule entries add to the stream (ScheduleEntry.add)
         self.embedding: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
         self.head_is_tied = False
@@ -66,6 +67,8 @@ class DecoderModel:
         out = [ParamSpec(s.embedding_name, (s.vocab_size, s.hidden_size), role="matrix")]
         if self.position is not None:
             out.extend(self.position.all_params())
+        for name, rows in s.stream_tables.items():
+            out.append(ParamSpec(name, (int(rows), s.hidden_size), role="vector", std=0.02))
         for b in self.blocks:
             out.extend(b.all_params())
         out.extend(self.final_norm.all_params())
@@ -81,6 +84,7 @@ class DecoderModel:
         self.embedding = tensors.pop(s.embedding_name)
         if self.position is not None:
             self.position.bind_all(tensors)
+        self.stream_tables = {name: tensors.pop(name) for name in s.stream_tables}
         for b in self.blocks:
             b.bind_all(tensors)
         self.final_norm.bind_all(tensors)
@@ -140,8 +144,15 @@ class DecoderModel:
         carry = None
         last = len(s.schedule) - 1
         for i, e in enumerate(s.schedule):
-            # a block is told the first norm of the block that runs next, so that it can apply it in its own tail
-            next_entry = self.blocks[s.schedule[i + 1].block].entry() if i < last else None
+            if e.add is not None:
+                # a vector joins the stream before this block: whatever the block before still holds goes in first
+                if carry is not None and carry.delta is not None:
+                    K.residual_add(x32, carry.delta)
+                carry = None
+                K.add_row(x32.view(-1, s.hidden_size), self.stream_tables[e.add[0]][int(e.add[1])])
+            # a block is told the first norm of the block that runs next, so that it can apply it in its own tail (not
+            # when something else is added to the stream in between)
+            next_entry = self.blocks[s.schedule[i + 1].block].entry() if i < last and s.schedule[i + 1].add is None else None
             x32, carry = self.blocks[e.block].forward(x32, ctx, caches[i], carry, next_entry)
             if self.observer is not None:
                 self.observer(i, x32, carry)

@@ -21,7 +21,15 @@ Further options of the spec, all off by default:
 * ``value_dim``: values (and the heads of the output) of another size than queries and keys.  The cache, and the
   kernels, have one head size: queries, keys and values are padded with zero rows of their matrices up to the larger
   of the two (rounded up to a multiple of 16), and the output map gets zero columns there, which changes no sum;
-* ``suffixes``: what follows a stem in the names of weights and biases.
+* ``suffixes``: what follows a stem in the names of weights and biases;
+* ``conv`` (taps > 1): a short causal convolution over time on every channel of q, k and v, right after the projection
+  (with its bias) and before anything else: ``u'_t = sum_j w[:, j] u_(t - taps + 1 + j)`` with zeros before the
+  sequence's start, no bias, no activation; the weights ``[channels, taps]`` are stored under the stem of q, k and v plus
+  ``conv_suffix`` (default ``.conv``).  The last ``taps - 1`` projected rows of a request are state of fixed size: the
+  mixer then asks for pages and a state slot;
+* ``qk_norm`` (a mapping with the tensor names ``q`` and ``k`` below the prefix, and ``eps``): an RMS norm per head on
+  queries and keys, its weight of head size shared by the heads, after the convolution and before the rotation;
+* ``keep_first`` (with a window): the first keys of a sequence stay visible behind the window, at their own positions.
 """
 
 from __future__ import annotations
@@ -32,7 +40,7 @@ import torch
 
 from .. import kernels as K
 from ..weights.loader import ParamSpec
-from .base import MIXERS, POSITIONS, Mixer, PagedKV
+from .base import MIXERS, POSITIONS, FixedState, Mixer, PagedKV
 from .linear import FusedLinear, undefer
 
 
@@ -57,6 +65,10 @@ class PagedAttention(Mixer):
             raise ValueError(f"{len(slopes)} distance slopes for {self.num_heads} heads")
         self.slopes = torch.tensor([float(x) for x in slopes], dtype=torch.float32, device=self.device) if slopes is not None else None
         self.window = spec.get("window")
+        self.keep_first = int(spec.get("keep_first") or 0) if self.window else 0
+        self.taps = int(spec.get("conv") or 1)
+        qk_norm = spec.get("qk_norm")
+        self.qk_norm_eps = float(qk_norm["eps"]) if qk_norm else 0.0
         if self.num_heads % self.num_kv_heads:
             raise ValueError(f"{self.num_heads} heads are not a multiple of {self.num_kv_heads} key/value heads")
         names = spec.get("names", {})
@@ -73,9 +85,21 @@ class PagedAttention(Mixer):
         self.gate = FusedLinear(prefix, [gate], self.hidden, [self.num_heads], False, dtype, suffixes=suffixes) if gate else None
         position = spec.get("position")
         self.position = POSITIONS.build(position, prefix, dtype, device, head_dim=self.head_dim) if position is not None else None
+        stems = [names.get("q", "q_proj"), names.get("k", "k_proj"), names.get("v", "v_proj")]
+        self.conv_names = [prefix + n + str(spec.get("conv_suffix", ".conv")) for n in stems] if self.taps > 1 else []
+        self.norm_names = [prefix + str(qk_norm[n]) for n in ("q", "k")] if qk_norm else []
+        self.conv_weight = self.q_norm = self.k_norm = None
+        # what the q|k|v product's epilogues cannot do goes through a kernel of its own behind a plain product
+        self.post = self.taps > 1 or bool(qk_norm)
+        # steps of single tokens read the convolution's state through the step's device tensors: they can be captured
+        self.decodes_from_device = self.taps > 1
+        self.real_outs = (self.num_heads * self.qk_dim, self.num_kv_heads * self.qk_dim, self.num_kv_heads * self.value_dim)
 
     def params(self) -> List[ParamSpec]:
-        return self.qkv.params() + self.out.params() + (self.gate.params() if self.gate is not None else [])
+        out = self.qkv.params() + self.out.params() + (self.gate.params() if self.gate is not None else [])
+        out += [ParamSpec(n, (o, self.taps), role="vector", mean=1.0 / self.taps, std=0.2) for n, o in zip(self.conv_names, self.real_outs)]
+        out += [ParamSpec(n, (self.qk_dim,), role="vector", init="ones_normal") for n in self.norm_names]
+        return out
 
     def parts(self):
         return [self.position] if self.position is not None else []
@@ -85,8 +109,23 @@ class PagedAttention(Mixer):
         self.out.bind(tensors)
         if self.gate is not None:
             self.gate.bind(tensors)
+        conv = [tensors.pop(n) for n in self.conv_names]
+        norms = [tensors.pop(n) for n in self.norm_names]
         if self.head_dim != self.qk_dim or self.head_dim != self.value_dim:
             self._pad_heads()
+            shapes = ((self.num_heads, self.qk_dim), (self.num_kv_heads, self.qk_dim), (self.num_kv_heads, self.value_dim))
+            conv = [self._pad_rows(t, *sh) for t, sh in zip(conv, shapes)]
+            norms = [torch.cat([t, torch.zeros(self.head_dim - self.qk_dim, dtype=t.dtype, device=t.device)]) for t in norms]
+        if conv:
+            self.conv_weight = torch.cat(conv, dim=0).contiguous()
+        if norms:
+            self.q_norm, self.k_norm = (t.contiguous() for t in norms)
+
+    def _pad_rows(self, t, heads, d):
+        """Rows of a per-channel tensor [heads * d, ...] with zero rows up to the one head size of the cache."""
+        out = torch.zeros((heads, self.head_dim) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        out[:, :d] = t.view(heads, d, *t.shape[1:])
+        return out.view(heads * self.head_dim, *t.shape[1:])
 
     def _pad_heads(self) -> None:
         """Zero rows (q, k, v, with their biases) and zero columns (output map) up to the one head size of the cache."""
@@ -114,13 +153,21 @@ class PagedAttention(Mixer):
         self.out.in_features = nh * D
 
     def cache_requirement(self):
-        return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+        paged = PagedKV(self.num_kv_heads, self.head_dim, self.window, self.keep_first)
+        if self.taps > 1:
+            # behind the pages: the last taps - 1 rows of the q|k|v projection, which the convolution of the next step reads
+            return (paged, FixedState(((self.taps - 1) * self.qkv_width,), torch.float32))
+        return paged
+
+    @property
+    def qkv_width(self) -> int:
+        return (self.num_heads + 2 * self.num_kv_heads) * self.head_dim
 
     def fused_decode(self):
         rope = self.position.fused_decode() if self.position is not None else None
         if type(self) is not PagedAttention or rope is None or rope["rotary_dim"] != self.head_dim or self.out.bias is not None:
             return None
-        if self.softcap or self.slopes is not None or self.gate is not None or self.value_dim != self.qk_dim:
+        if self.softcap or self.slopes is not None or self.gate is not None or self.value_dim != self.qk_dim or self.post or self.keep_first:
             return None
         return {"w_qkv": self.qkv.weight, "b_qkv": self.qkv.bias, "w_o": self.out.weight, "hidden": self.hidden, "heads": self.num_heads,
                 "kv_heads": self.num_kv_heads, "head_dim": self.head_dim, "scale": self.scale, "window": self.window,
@@ -134,20 +181,34 @@ class PagedAttention(Mixer):
 
     def _attend(self, h, ctx, cache):
         """Everything before the output projection: [tokens, heads * head_dim]."""
+        state = None
+        if self.taps > 1:
+            cache, state = cache.parts                                 # pages, and the convolution's rows behind them
         view = ctx.group(cache.group)
         gate = self.gate(h) if self.gate is not None else None        # (a deferred activation: the product applies its factor)
-        h, row_scale = undefer(h, self.qkv.weight)
-        qkv = torch.empty((h.shape[0], self.qkv.out_features), dtype=self.dtype, device=h.device)
-        # projection, position encoding of q and k, k and v into the cache: one call (and for few tokens one kernel)
         rot = self.position.rotary(ctx) if self.position is not None else None
-        K.linear_rope_kv(
-            h, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, rot.denominators if rot else None, rot.rotary_dim if rot else 0,
-            view.slot_mapping, cache.k, cache.v, self.num_heads, self.num_kv_heads, self.head_dim, cache.writes, row_scale=row_scale,
-            cos_sin=rot.table if rot else None)
+        if self.post:
+            # projection; then convolution, norm per head, rotation and the cache write as one kernel; then the state moves on
+            proj = self.qkv(h)
+            qkv = torch.empty_like(proj)
+            K.conv_norm_rope_kv(proj, qkv, self.conv_weight, state.state if state is not None else None, 0, ctx.q_start, ctx.seq_of_token,
+                                ctx.state_slots, self.q_norm, self.k_norm, self.qk_norm_eps, self.qk_dim, ctx.positions,
+                                rot.denominators if rot else None, rot.rotary_dim if rot else 0, view.slot_mapping, cache.k, cache.v,
+                                self.num_heads, self.num_kv_heads, self.head_dim, cache.writes)
+            if state is not None and state.writes:
+                K.conv_state_shift(proj, 0, self.qkv_width, self.taps, state.state, 0, ctx.q_start, ctx.state_slots)
+        else:
+            h, row_scale = undefer(h, self.qkv.weight)
+            qkv = torch.empty((h.shape[0], self.qkv.out_features), dtype=self.dtype, device=h.device)
+            # projection, position encoding of q and k, k and v into the cache: one call (and for few tokens one kernel)
+            K.linear_rope_kv(
+                h, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, rot.denominators if rot else None, rot.rotary_dim if rot else 0,
+                view.slot_mapping, cache.k, cache.v, self.num_heads, self.num_kv_heads, self.head_dim, cache.writes, row_scale=row_scale,
+                cos_sin=rot.table if rot else None)
         o = torch.empty((h.shape[0], self.q_dim), dtype=self.dtype, device=h.device)
         K.paged_attention(
             qkv, o, cache.k, cache.v, view.block_table, ctx.q_start, ctx.ctx_lens, ctx.seq_of_token, ctx.positions,
             self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window,
             ctx.max_q_len, ctx.max_ctx_len, old_lens=ctx.old_lens, singles=ctx.num_single,
-            units=ctx.attn_units, unit_slots=ctx.attn_unit_slots, softcap=self.softcap, slopes=self.slopes, gate=gate)
+            units=ctx.attn_units, unit_slots=ctx.attn_unit_slots, softcap=self.softcap, slopes=self.slopes, gate=gate, keep_first=self.keep_first)
         return o

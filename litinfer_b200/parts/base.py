@@ -56,11 +56,12 @@ from ..weights.loader import ParamSpec
 
 @dataclass(frozen=True)
 class PagedKV:
-    """Keys and values of every token (or of the last ``window``), in pages."""
+    """Keys and values of every token (or of the last ``window``, and with a window the first ``keep_first`` as well), in pages."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

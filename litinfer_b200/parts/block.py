@@ -161,3 +161,59 @@ class HyperPreNormBlock(Block):
         y = self.feed_forward.forward(h, ctx)
         h = self._write_back(xs, y, self.feed_forward_connection, nxt.norm if nxt else None, nxt.read if nxt else None)
         return xs, (Carry(normed=h) if h is not None else None)
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """A norm before and a norm after each sublayer: ``x += post(Mixer(pre(x)))``, then ``x += post'(FeedForward(pre'(x)))``.
+    Roles: ``mixer_norm``, ``mixer_post_norm``, and with a feed-forward ``feed_forward_norm``, ``feed_forward_post_norm``;
+    any registered norm that says what it is through ``statistics()`` (weight, centered or not, eps) serves in any role.
+
+    The norm after a sublayer, the addition to the stream and the norm before the next sublayer are one kernel and one
+    pass over the stream (``kernels.norm_add_norm``); told the next block's entry, the last sublayer's pass already
+    applies that block's first norm."""
+
+    def __init__(self, spec, prefix, dtype, device):
+        super().__init__(spec, prefix, dtype, device)
+        self.mixer_norm = self.build(NORMS, "mixer_norm")
+        self.mixer = self.build(MIXERS, "mixer")
+        self.mixer_post_norm = self.build(NORMS, "mixer_post_norm")
+        self.feed_forward = self.build(FEED_FORWARDS, "feed_forward", required=False)
+        self.feed_forward_norm = self.build(NORMS, "feed_forward_norm", required=self.feed_forward is not None)
+        self.feed_forward_post_norm = self.build(NORMS, "feed_forward_post_norm", required=self.feed_forward is not None)
+        for n in (self.mixer_norm, self.mixer_post_norm, self.feed_forward_norm, self.feed_forward_post_norm):
+            if n is not None and not hasattr(n, "statistics"):
+                raise ValueError(f"block 'sandwich' at {spec.prefix!r}: norm '{n.spec.kind}' does not say what it is (statistics())")
+
+    def parts(self) -> List:
+        return [p for p in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.feed_forward_norm, self.feed_forward,
+                            self.feed_forward_post_norm) if p is not None]
+
+    def entry(self):
+        return Tail(None, self.mixer_norm, False)
+
+    def _close(self, x32, y, post, nxt):
+        """x32 += post(y); the next norm of the sum if that norm is known and of a kind the kernel takes."""
+        if nxt is not None and hasattr(nxt, "statistics"):
+            out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+            K.norm_add_norm(x32, y, post.statistics(), nxt.statistics(), out)
+            return out
+        K.norm_add_norm(x32, y, post.statistics(), None, None)
+        return nxt.forward(x32) if nxt is not None else None
+
+    def forward(self, x32, ctx, cache, carry, next_entry=None):
+        if carry is None:
+            h = self.mixer_norm.forward(x32)
+        elif carry.normed is not None:
+            h = carry.normed
+        else:
+            h = self.mixer_norm.add_forward(x32, carry.delta)
+        nxt = next_entry.norm if next_entry is not None and type(next_entry) is Tail else None
+        y = self.mixer.forward(h, ctx, cache)
+        if self.feed_forward is None:
+            h = self._close(x32, y, self.mixer_post_norm, nxt)
+            return x32, (Carry(normed=h) if h is not None else None)
+        h = self._close(x32, y, self.mixer_post_norm, self.feed_forward_norm)
+        y = self.feed_forward.forward(h, ctx)
+        h = self._close(x32, y, self.feed_forward_post_norm, nxt)
+        return x32, (Carry(normed=h) if h is not None else None)

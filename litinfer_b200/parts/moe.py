@@ -1,0 +1,94 @@
+"""A mixture of experts: many small gated feed-forward layers, of which each token uses a few.
+
+    z = W_router h                      (float32 logits)
+    s = sigmoid(z)                      the scores; the ``top`` largest choose a token's experts (``scoring``: sigmoid)
+    w_e = s_e                           their weights: the scores as they are (``renormalize``: divided by their sum)
+    y = sum_e expert_e(w_e h)           ``weight_on`` "input"; or  y = sum_e w_e expert_e(h)  with "output"
+    expert(u) = W_down (silu(W_gate u) * (W_up u)), no biases.
+
+How a step runs it: the router's product with a float32 result, the choice per token (one warp a token), a stable
+counting sort of the (token, choice) pairs by expert on the device, one gather that builds the experts' input rows in
+sorted order (with the weight on them), a product per expert over its run of rows for gate|up and for down
+(``kernels.grouped_linear`` with the row offsets the sort left on the device), and a combine that sums a token's rows in
+the order of its choices.  Nothing comes back to the host, so the launches are the same whatever the routing, and a step
+of single tokens can be captured.  A row's result does not depend on which rows share its expert.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .. import kernels as K
+from ..weights.loader import ParamSpec
+from .base import FEED_FORWARDS, FeedForward
+from .linear import FusedLinear
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    def __init__(self, spec, prefix, dtype, device):
+        super().__init__(spec, prefix, dtype, device)
+        self.hidden = int(spec["hidden_size"])
+        self.intermediate = int(spec["intermediate_size"])
+        self.experts = int(spec["experts"])
+        self.top = int(spec["top"])
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"{self.top} of {self.experts} experts")
+        if spec.get("scoring", "sigmoid") != "sigmoid":
+            raise ValueError(f"routing by '{spec.get('scoring')}' is not supported (sigmoid)")
+        self.renormalize = bool(spec.get("renormalize", False))
+        if self.renormalize:
+            raise ValueError("renormalised routing weights are not supported")
+        self.weight_on = str(spec.get("weight_on", "output"))
+        if self.weight_on not in ("input", "output"):
+            raise ValueError(f"weight_on must be 'input' or 'output', got {self.weight_on!r}")
+        n = dict(spec.get("names", {}))
+        suffixes = tuple(spec.get("suffixes", (".weight", ".bias")))
+        self.router = FusedLinear(prefix, [n.get("router", "gate")], self.hidden, [self.experts], False, dtype, suffixes=suffixes)
+        stem = n.get("expert", "experts.{}.")                 # the e-th expert's tensors start with prefix + stem.format(e)
+        w = suffixes[0]
+        self.expert_names = [tuple(prefix + stem.format(e) + n.get(k, d) + w for k, d in (("gate", "gate_proj"), ("up", "up_proj"), ("down", "down_proj")))
+                             for e in range(self.experts)]
+        self.gate_up = self.down = None                       # [E, 2 F, hidden] (gate rows, then up rows) and [E, hidden, F]
+
+    def params(self) -> List[ParamSpec]:
+        out = self.router.params()
+        F, W = self.intermediate, self.hidden
+        for g, u, d in self.expert_names:
+            out += [ParamSpec(g, (F, W), role="matrix"), ParamSpec(u, (F, W), role="matrix"), ParamSpec(d, (W, F), role="matrix")]
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.router.bind(tensors)
+        gu, dn = [], []
+        for g, u, d in self.expert_names:
+            gu.append(torch.cat([tensors.pop(g), tensors.pop(u)], dim=0))
+            dn.append(tensors.pop(d))
+        self.gate_up = torch.stack(gu).contiguous()
+        self.down = torch.stack(dn).contiguous()
+
+    def forward(self, h, ctx):
+        T = h.shape[0]
+        E, top, F = self.experts, self.top, self.intermediate
+        dev = h.device
+        logits = self.router(h, out_dtype=torch.float32)
+        ids = torch.empty((T, top), dtype=torch.int32, device=dev)
+        weights = torch.empty((T, top), dtype=torch.float32, device=dev)
+        K.moe_route(logits, top, ids, weights)
+        offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        pair_at = torch.empty(T * top, dtype=torch.int32, device=dev)
+        place_of = torch.empty(T * top, dtype=torch.int32, device=dev)
+        K.moe_sort(ids, E, offsets, pair_at, place_of)
+        on_input = self.weight_on == "input"
+        rows = torch.empty((T * top, self.hidden), dtype=self.dtype, device=dev)
+        K.moe_gather(h, pair_at, weights if on_input else None, top, rows)
+        both = torch.empty((T * top, 2 * F), dtype=self.dtype, device=dev)
+        K.grouped_linear(rows, self.gate_up, both, offsets)
+        act = torch.empty((T * top, F), dtype=self.dtype, device=dev)
+        K.swiglu(both, act)
+        K.grouped_linear(act, self.down, rows, offsets)
+        y = torch.empty((T, self.hidden), dtype=self.dtype, device=dev)
+        K.moe_combine(rows, place_of, None if on_input else weights, top, y)
+        return y

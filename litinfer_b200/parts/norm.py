@@ -43,6 +43,10 @@ class RMSNorm(Norm):
     def fused_decode(self):
         return {"weight": self.weight, "eps": self.eps, "size": self.size} if type(self) is RMSNorm and self.weight is not None else None
 
+    def statistics(self):
+        """(weight, centered, eps) as :func:`litinfer_b200.kernels.norm_add_norm` takes a norm: not centered."""
+        return (self.weight, False, self.eps)
+
     def forward(self, x32):
         out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
         K.rmsnorm(x32, self.weight, self.eps, out)
@@ -78,4 +82,42 @@ class RMSNorm(Norm):
     def gather_forward(self, x32, rows):
         out = torch.empty((rows.shape[0], x32.shape[1]), dtype=self.dtype, device=x32.device)
         K.gather_rmsnorm(x32, rows, self.weight, self.eps, out)
+        return out
+
+
+@NORMS.register("layernorm")
+class LayerNorm(Norm):
+    """Layer norm with a weight and no bias: ``y = (x - mean(x)) / sqrt(var(x) + eps) * w`` with the variance the mean of
+    the squared deviations; mean, variance and products in float32, one rounding to the run dtype.  Every form is the one
+    kernel that also serves an arrangement with norms on both sides of a sublayer (``kernels.norm_add_norm``)."""
+
+    def __init__(self, spec, prefix, dtype, device):
+        super().__init__(spec, prefix, dtype, device)
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.tensor = self.prefix + str(spec.get("tensor", "weight"))
+        self.weight = None
+
+    def params(self) -> List[ParamSpec]:
+        return [ParamSpec(self.tensor, (self.size,), role="vector", init="ones_normal")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors.pop(self.tensor)
+
+    def statistics(self):
+        return (self.weight, True, self.eps)
+
+    def forward(self, x32):
+        out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+        K.norm_add_norm(x32, None, None, self.statistics(), out)
+        return out
+
+    def add_forward(self, x32, delta):
+        out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+        K.norm_add_norm(x32, delta, None, self.statistics(), out)
+        return out
+
+    def gather_forward(self, x32, rows):
+        out = torch.empty((rows.shape[0], x32.shape[1]), dtype=self.dtype, device=x32.device)
+        K.norm_add_norm(x32, None, None, self.statistics(), out, rows=rows)
         return out

@@ -146,7 +146,7 @@ def rope_table(positions, denominators, out):
 
 def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
                     num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len, implementation=None, old_lens=None, singles=0,
-                    units=None, unit_slots=(0, 0), softcap=0.0, slopes=None, gate=None):
+                    units=None, unit_slots=(0, 0), softcap=0.0, slopes=None, gate=None, keep_first=0, sinks=None):
     # old_lens only tells a kernel which keys it may read early, singles which kernel takes which sequence, units how a
     # kernel shares its work out; the result does not depend on them
     T = qkv.shape[0]
@@ -160,6 +160,8 @@ def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, 
         s, p = seqs[t], poss[t]
         lo = 0 if not window else max(0, p - window + 1)
         keys = torch.arange(lo, p + 1, device=qkv.device)
+        if keep_first and lo > 0:
+            keys = torch.cat([torch.arange(0, min(keep_first, lo), device=qkv.device), keys])
         pages = block_table[s].long()[keys // page_size]
         offs = keys % page_size
         k = k_cache[pages, :, offs].float()          # [n, kv_heads, dh]
@@ -170,7 +172,10 @@ def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, 
                 sc = softcap * torch.tanh(sc / softcap)
             if slopes is not None:
                 sc = sc - slopes[h] * (p - keys).float()
-            pr = torch.softmax(sc, dim=0)
+            if sinks is not None:
+                pr = torch.softmax(torch.cat([sc, sinks[h:h + 1].float()]), dim=0)[:-1]
+            else:
+                pr = torch.softmax(sc, dim=0)
             res[t, h] = pr @ v[:, h // group]
             if gate is not None:
                 res[t, h] *= torch.sigmoid(gate[t, h].float())
@@ -179,7 +184,7 @@ def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, 
 
 def paged_attention_dense(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
                           num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len, implementation=None, old_lens=None,
-                          singles=0, units=None, unit_slots=(0, 0), softcap=0.0, slopes=None, gate=None):
+                          singles=0, units=None, unit_slots=(0, 0), softcap=0.0, slopes=None, gate=None, keep_first=0, sinks=None):
     """The same formula as :func:`paged_attention`, a sequence at a time instead of a token and a head at a time (for
     contexts of thousands of keys): scores of all the sequence's tokens against all its keys in float32, keys outside
     [p - window + 1, p] masked, softmax, weighted sum."""
@@ -206,12 +211,139 @@ def paged_attention_dense(qkv, out, k_cache, v_cache, block_table, q_start, ctx_
             sc = sc - slopes[:, None, None] * (pos[:, None] - keys[None, :]).float()[None]
         seen = keys[None, :] <= pos[:, None]
         if window:
-            seen &= keys[None, :] > pos[:, None] - window
+            inside = keys[None, :] > pos[:, None] - window
+            if keep_first:
+                inside |= keys[None, :] < keep_first
+            seen &= inside
         sc = sc.masked_fill(~seen[None], float("-inf"))
-        res[lo:hi] = torch.einsum("htc,chd->thd", torch.softmax(sc, dim=-1), v)
+        if sinks is not None:
+            sk = sinks.float()[:, None, None].expand(num_heads, hi - lo, 1)
+            pr = torch.softmax(torch.cat([sc, sk], dim=-1), dim=-1)[..., :-1]
+        else:
+            pr = torch.softmax(sc, dim=-1)
+        res[lo:hi] = torch.einsum("htc,chd->thd", pr, v)
         if gate is not None:
             res[lo:hi] *= torch.sigmoid(gate[lo:hi].float())[:, :, None]
     _store(out, res.reshape(T, num_heads * head_dim))
+
+
+def _norm_of(v, spec):
+    weight, centered, eps = spec
+    v = v.float()
+    if centered:
+        v = v - v.mean(-1, keepdim=True)
+    return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * weight
+
+
+def norm_add_norm(x32, y, post, nxt, out, rows=None):
+    if y is not None:
+        x32.add_(_norm_of(y, post) if post is not None else y.float())
+    if nxt is not None:
+        _store(out, _norm_of(x32 if rows is None else x32[rows.long()], nxt))
+
+
+def add_row(x32, row):
+    x32.add_(row)
+
+
+def rmsnorm_cols(x, col, n, width, weight, eps, out, col_a, col_b=-1):
+    v = x[:, col:col + n].float()
+    r = (v / torch.sqrt((v * v).sum(-1, keepdim=True) / width + eps) * weight).to(out.dtype)
+    out[:, col_a:col_a + n] = r
+    if col_b >= 0:
+        out[:, col_b:col_b + n] = r
+
+
+def conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, positions,
+                      denominators, rotary_dim, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim, write=True):
+    T, N = proj.shape
+    u = proj.float()
+    if conv_w is not None and conv_w.shape[1] > 1:
+        taps = conv_w.shape[1]
+        starts, sl = q_start.tolist(), slots.tolist()
+        res = torch.zeros_like(u)
+        for s in range(len(starts) - 1):
+            lo, hi = starts[s], starts[s + 1]
+            if hi == lo:
+                continue
+            old = state[sl[s], state_off:state_off + (taps - 1) * N].view(taps - 1, N)
+            padded = torch.cat([old, u[lo:hi]], dim=0)
+            for j in range(taps):
+                res[lo:hi] += padded[j:j + hi - lo] * conv_w[:, j]
+        u = res
+    q_dim, kv_dim = num_heads * head_dim, num_kv_heads * head_dim
+    half = rotary_dim // 2
+    if rotary_dim:
+        phi = positions.float()[:, None] / denominators[None, :]
+        cos, sin = torch.cos(phi)[:, None, :], torch.sin(phi)[:, None, :]
+
+    def shape(x, weight):
+        x = x.clone()
+        if weight is not None:
+            x = x / torch.sqrt((x * x).sum(-1, keepdim=True) / norm_width + eps) * weight
+        if rotary_dim:
+            a, b = x[..., :half].clone(), x[..., half:rotary_dim].clone()
+            x[..., :half] = a * cos - b * sin
+            x[..., half:rotary_dim] = b * cos + a * sin
+        return x
+
+    out[:, :q_dim] = shape(u[:, :q_dim].reshape(T, num_heads, head_dim), q_norm).reshape(T, q_dim).to(out.dtype)
+    if not write:
+        return
+    k = shape(u[:, q_dim:q_dim + kv_dim].reshape(T, num_kv_heads, head_dim), k_norm).to(out.dtype)
+    v = u[:, q_dim + kv_dim:].reshape(T, num_kv_heads, head_dim).to(out.dtype)
+    page_size = k_cache.shape[2]
+    page = (slot_mapping // page_size).long()
+    off = (slot_mapping % page_size).long()
+    k_cache[page, :, off] = k
+    v_cache[page, :, :, off] = v
+
+
+def grouped_linear(a, weight, out, row_offsets=None, a_group_cols=0, out_group_cols=0):
+    G, N, Kd = weight.shape
+    if row_offsets is not None:
+        offs = row_offsets.tolist()
+        for g in range(G):
+            lo, hi = offs[g], offs[g + 1]
+            if hi > lo:
+                out[lo:hi] = (a[lo:hi].float() @ weight[g].float().t()).to(out.dtype)
+        return
+    for g in range(G):
+        out[:, g * out_group_cols:g * out_group_cols + N] = (a[:, g * a_group_cols:g * a_group_cols + Kd].float() @ weight[g].float().t()).to(out.dtype)
+
+
+def moe_route(logits, top, ids, weights):
+    s = torch.sigmoid(logits.float())
+    E = s.shape[1]
+    # the largest scores, the lower index first among equals
+    order = torch.sort(s - torch.arange(E, device=s.device) * 0.0, dim=-1, descending=True, stable=True)
+    ids.copy_(order.indices[:, :top].to(torch.int32))
+    weights.copy_(order.values[:, :top])
+
+
+def moe_sort(ids, experts, offsets, pair_at, place_of):
+    flat = ids.reshape(-1).long()
+    order = torch.sort(flat, stable=True).indices
+    pair_at.copy_(order.to(torch.int32))
+    place_of[order] = torch.arange(flat.numel(), dtype=torch.int32, device=ids.device)
+    counts = torch.bincount(flat, minlength=experts)
+    offsets[0] = 0
+    offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
+
+
+def moe_gather(h, pair_at, weights, top, out):
+    src = h[(pair_at // top).long()].float()
+    if weights is not None:
+        src = src * weights.reshape(-1)[pair_at.long()][:, None]
+    _store(out, src)
+
+
+def moe_combine(rows, place_of, weights, top, y):
+    T, H = y.shape
+    r = rows[place_of.long()].float().view(T, top, H)
+    if weights is not None:
+        r = r * weights[:, :, None]
+    _store(y, r.sum(1))
 
 
 def gather_rows(src, rows, out):
@@ -433,6 +565,7 @@ def table_gather(resident, updates, slots, out, trash_page):
             out[s, b] = resident[slot, b] if b < cols else trash_page
 
 
-ALL = ["glu_clamped", "weighted_sum2", "add_position_rows", "hc_expand", "hc_read_norm", "hc_update", "causal_conv_silu", "conv_state_shift", "ssm_scan",
+ALL = ["norm_add_norm", "add_row", "rmsnorm_cols", "conv_norm_rope_kv", "grouped_linear", "moe_route", "moe_sort", "moe_gather", "moe_combine",
+       "glu_clamped", "weighted_sum2", "add_position_rows", "hc_expand", "hc_read_norm", "hc_update", "causal_conv_silu", "conv_state_shift", "ssm_scan",
        "decay_scan", "gated_rmsnorm", "table_gather", "gather_rows", "scale_inplace", "logit_cap", "rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]
