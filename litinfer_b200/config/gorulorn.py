@@ -116,7 +116,7 @@ class GorulornConfig:
             if dims % 2 or dims > dim:
                 raise ConfigError(f"config.json: {where}rot.dims {dims} must be even and at most dim {dim}")
             position = PartSpec("rope", {"theta": _float(rot, "base", where + "rot."), "rotary_dim": dims})
-        taps = _opt_int(m, "conv", where) or 1
+        taps = _opt_int(m, "conv", where)                       # none: no convolution (and no such tensors)
         return PartSpec("attention", {
             "hidden_size": self.width, "num_heads": heads, "num_kv_heads": kv, "head_dim": dim, "value_dim": _opt_int(m, "vdim", where) or dim,
             "scale": _float(m, "scale", where, 1.0 / math.sqrt(dim)), "window": window, "keep_first": keep, "qkv_bias": True, "out_bias": False,

@@ -9,7 +9,7 @@
 //      angle float(pos) / denom[j]);
 //   4. q written to `out` (the q columns of a [T, (nh + 2 nkv) dh] row), k and v into the paged cache (values transposed).
 //
-// Each step is optional (taps <= 1, null norm weights, rotary_dim 0).  One warp per (token, head of q|k|v); the head's
+// Each step is optional (no convolution weights, null norm weights, rotary_dim 0).  One warp per (token, head of q|k|v); the head's
 // elements stay in registers, the rotation's partners meet through shared memory.  Convolution, norm and angles are
 // computed in float from run-dtype inputs and rounded once.  The state itself is moved on by li_conv_state_shift.
 #include "common.cuh"
@@ -42,11 +42,11 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
     const int per = (dh + 31) >> 5;
     float v[kPerLane];
     // 1. the convolution (or the plain value)
-    if (taps > 1) {
+    if (conv_w != nullptr) {
         const int s = seq_of_token[t];
         const int q0 = q_start[s];
         const int li = t - q0;
-        const float* st = state + (size_t)slots[s] * state_stride + state_off;
+        const float* st = taps > 1 ? state + (size_t)slots[s] * state_stride + state_off : nullptr;      // one tap reads no older row
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) {
             const int d = lane + 32 * i;
@@ -138,7 +138,7 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
 }  // namespace
 
 // proj, out: [T, (nh + 2 nkv) dh] in the run dtype (out may not be proj when taps > 1: tokens read their neighbours' rows).
-// conv_w [(nh + 2 nkv) dh, taps] float (NULL or taps <= 1: no convolution); state [slots, state_stride] float with the
+// conv_w [(nh + 2 nkv) dh, taps] float (NULL: no convolution; one tap: a factor per channel, no state); state [slots, state_stride] float with the
 // convolution's rows at state_off; q_norm, k_norm [dh] float (NULL: no norm), the mean of squares over norm_width
 // elements (dh, or fewer when heads are padded with zeros); rotary_dim 0: no rotation.  write 0: only q is made.
 LI_EXPORT int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* conv_w, int taps, const float* state,
@@ -151,7 +151,8 @@ LI_EXPORT int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const
     LI_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= dh, "conv_norm_rope_kv: rotary_dim %d must be even and at most head_dim %d",
                rotary_dim, dh);
     LI_REQUIRE(rotary_dim == 0 || denom != nullptr, "conv_norm_rope_kv: rotary_dim %d without denominators", rotary_dim);
-    LI_REQUIRE(taps <= 1 || (conv_w != nullptr && state != nullptr && proj != out), "conv_norm_rope_kv: a convolution needs weights, a state and an output of its own");
+    LI_REQUIRE(taps >= 1 && (taps == 1 || (conv_w != nullptr && state != nullptr && proj != out)),
+               "conv_norm_rope_kv: a convolution over %d taps needs weights, a state and an output of its own", taps);
     LI_REQUIRE((q_norm == nullptr) == (k_norm == nullptr), "conv_norm_rope_kv: queries and keys are normalised together or not at all");
     LI_REQUIRE(norm_width > 0 && norm_width <= dh, "conv_norm_rope_kv: bad norm width %d", norm_width);
     LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "conv_norm_rope_kv: unknown dtype %d", dtype);

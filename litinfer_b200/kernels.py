@@ -802,7 +802,8 @@ def conv_norm_rope_kv(proj: torch.Tensor, out: torch.Tensor, conv_w: Optional[to
                       v_cache: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, write: bool = True) -> None:
     """What stands between a q|k|v product ``proj`` [T, (heads + 2 kv_heads) head_dim] and attention: a causal convolution
     per channel over the last ``taps`` projected rows (``conv_w`` float32 [channels, taps], the last column the token's own;
-    rows before a portion come from ``state[slot, state_off:]`` as [taps - 1, channels], oldest first; None: none), an RMS
+    rows before a portion come from ``state[slot, state_off:]`` as [taps - 1, channels], oldest first; one tap is a factor
+    per channel and reads no state; None: no convolution), an RMS
     norm per query and key head (``q_norm``, ``k_norm`` [head_dim], the mean over ``norm_width`` elements; None: none), the
     rotation of the first ``rotary_dim`` elements of queries and keys; queries to the q columns of ``out``, keys and values
     into the paged cache.  The state is not changed (:func:`conv_state_shift` moves it on)."""
@@ -837,7 +838,7 @@ def conv_norm_rope_kv(proj: torch.Tensor, out: torch.Tensor, conv_w: Optional[to
     if nkv != num_kv_heads or dh != head_dim:
         raise KernelError(f"cache of {nkv} heads x {dh} does not match {num_kv_heads} x {head_dim}")
     _check(library().li_conv_norm_rope_kv(
-        _p(proj), _p(out), _i(_dt(proj)), _p(conv_w if taps > 1 else None), _i(taps), st, stride, off, _p(q_start), _p(seq_of_token), _p(slots),
+        _p(proj), _p(out), _i(_dt(proj)), _p(conv_w), _i(taps), st, stride, off, _p(q_start), _p(seq_of_token), _p(slots),
         _p(q_norm), _p(k_norm), _f(eps), _i(int(norm_width)), _p(positions), _p(denominators if rotary_dim else None), _i(rotary_dim),
         _p(slot_mapping), _p(k_cache), _p(v_cache), _i(T), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages),
         _i(1 if write else 0), _stream(out)), "conv_norm_rope_kv")

@@ -22,7 +22,7 @@ Further options of the spec, all off by default:
   kernels, have one head size: queries, keys and values are padded with zero rows of their matrices up to the larger
   of the two (rounded up to a multiple of 16), and the output map gets zero columns there, which changes no sum;
 * ``suffixes``: what follows a stem in the names of weights and biases;
-* ``conv`` (taps > 1): a short causal convolution over time on every channel of q, k and v, right after the projection
+* ``conv`` (taps; one tap is a learned factor per channel): a short causal convolution over time on every channel of q, k and v, right after the projection
   (with its bias) and before anything else: ``u'_t = sum_j w[:, j] u_(t - taps + 1 + j)`` with zeros before the
   sequence's start, no bias, no activation; the weights ``[channels, taps]`` are stored under the stem of q, k and v plus
   ``conv_suffix`` (default ``.conv``).  The last ``taps - 1`` projected rows of a request are state of fixed size: the
@@ -66,7 +66,7 @@ class PagedAttention(Mixer):
         self.slopes = torch.tensor([float(x) for x in slopes], dtype=torch.float32, device=self.device) if slopes is not None else None
         self.window = spec.get("window")
         self.keep_first = int(spec.get("keep_first") or 0) if self.window else 0
-        self.taps = int(spec.get("conv") or 1)
+        self.taps = int(spec.get("conv") or 0)                # 0: no convolution
         qk_norm = spec.get("qk_norm")
         self.qk_norm_eps = float(qk_norm["eps"]) if qk_norm else 0.0
         if self.num_heads % self.num_kv_heads:
@@ -86,11 +86,11 @@ class PagedAttention(Mixer):
         position = spec.get("position")
         self.position = POSITIONS.build(position, prefix, dtype, device, head_dim=self.head_dim) if position is not None else None
         stems = [names.get("q", "q_proj"), names.get("k", "k_proj"), names.get("v", "v_proj")]
-        self.conv_names = [prefix + n + str(spec.get("conv_suffix", ".conv")) for n in stems] if self.taps > 1 else []
+        self.conv_names = [prefix + n + str(spec.get("conv_suffix", ".conv")) for n in stems] if self.taps >= 1 else []
         self.norm_names = [prefix + str(qk_norm[n]) for n in ("q", "k")] if qk_norm else []
         self.conv_weight = self.q_norm = self.k_norm = None
         # what the q|k|v product's epilogues cannot do goes through a kernel of its own behind a plain product
-        self.post = self.taps > 1 or bool(qk_norm)
+        self.post = self.taps >= 1 or bool(qk_norm)
         # steps of single tokens read the convolution's state through the step's device tensors: they can be captured
         self.decodes_from_device = self.taps > 1
         self.real_outs = (self.num_heads * self.qk_dim, self.num_kv_heads * self.qk_dim, self.num_kv_heads * self.value_dim)

@@ -258,7 +258,7 @@ def conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token
                       denominators, rotary_dim, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim, write=True):
     T, N = proj.shape
     u = proj.float()
-    if conv_w is not None and conv_w.shape[1] > 1:
+    if conv_w is not None:
         taps = conv_w.shape[1]
         starts, sl = q_start.tolist(), slots.tolist()
         res = torch.zeros_like(u)
@@ -266,7 +266,7 @@ def conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token
             lo, hi = starts[s], starts[s + 1]
             if hi == lo:
                 continue
-            old = state[sl[s], state_off:state_off + (taps - 1) * N].view(taps - 1, N)
+            old = state[sl[s], state_off:state_off + (taps - 1) * N].view(taps - 1, N) if taps > 1 else u[:0]
             padded = torch.cat([old, u[lo:hi]], dim=0)
             for j in range(taps):
                 res[lo:hi] += padded[j:j + hi - lo] * conv_w[:, j]
