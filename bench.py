@@ -25,8 +25,8 @@ Weights (3 GB) are larger than L2, so nothing stays cached between steps.
 profiling runs and the summaries under ``profiles/``); ``mixed`` is a step of ``--batch`` requests decoding at
 ``--context`` beside a portion of ``--prefill-tokens`` prompt tokens.
 
-``--only design`` runs the Filasun design beside the Qwen2 model of equal layer sizes and layer count (``--design-shapes``,
-``--layers``, default 6): prefill of ``--prefill-tokens`` tokens and decode at batch 1, 8 and 32; ``--arch filasun`` puts
+``--only design`` runs a design (``--design filasun|gorulorn``, default filasun) beside the Qwen2 model of equal layer sizes and layer count (``--design-shapes``,
+``--layers``, default 6): prefill of ``--prefill-tokens`` tokens and decode at batch 1, 8 and 32; ``--arch filasun|gorulorn`` puts
 that design behind ``--only decode|prefill|kernels-decode|kernels-prefill`` (the kernel tables of ``profiles/``).
 
 ``--shape 1.5b|7b|14b`` chooses the layer sizes (default 1.5b, the headline; the other two are the larger workloads of
@@ -106,25 +106,58 @@ def filasun_config(shape: str, layers: int, window: int = 1024):
             "max_positions": d["max_position_embeddings"], "norm": {"eps": 1e-5}, "streams": 4, "vocab": d["vocab_size"], "width": H}
 
 
+def gorulorn_config(shape: str, layers: int, window: int = 1024):
+    """A Gorulorn model with the layer sizes of a shape of the benchmark description: the same width, heads, key/value
+    heads, head size and vocabulary as the Qwen2 model of that shape.  Layers alternate between latent attention (at
+    most 16 heads, a query latent of half the width, a key/value latent of 128, a window of ``window``, sinks) and
+    grouped-query attention (a convolution of 4 taps, norms per head, half of each head rotated, a window of ``window``
+    that keeps the first 4 tokens); every layer has 8 experts of half the dense feed-forward width, 2 per token (the
+    same products per token as the dense model, four times its feed-forward weights).  The two layers in the middle
+    run twice (``layers`` + 2 layer runs)."""
+    d = SHAPES[shape]
+    H, nh, nkv, dh = d["hidden_size"], d["num_attention_heads"], d["num_key_value_heads"], d["head_dim"]
+    mlp = {"kind": "moe", "expert": {"ff": d["intermediate_size"] // 2}, "router": {"experts": 8, "top": 2}}
+    lat = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": min(nh, 16), "dim": dh, "vdim": dh, "q_rank": H // 2, "kv_rank": 128, "mask": {"size": window}, "scale": dh ** -0.5}}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": nh, "kv_heads": nkv, "dim": dh, "vdim": dh, "conv": 4, "mask": {"size": window, "keep_first": 4},
+                     "rot": {"dims": dh // 2, "base": d["rope_theta"]}, "scale": dh ** -0.5}}
+    mid = max(0, layers // 2 - 1)
+    return {"architecture": "Gorulorn", "layers": [lat if i % 2 == 0 else att for i in range(layers)], "norm": {"eps": 1e-5},
+            "loop": {"start": mid, "stop": min(layers, mid + 2), "times": 2}, "vocab": d["vocab_size"], "width": H,
+            "max_positions": d["max_position_embeddings"]}
+
+
+def design_layer_runs(cfg) -> int:
+    loop = cfg.get("loop")
+    return len(cfg["layers"]) + ((loop["stop"] - loop["start"]) * (loop["times"] - 1) if loop else 0)
+
+
 def time_design(args, peaks):
-    """Prefill and decode of the Filasun design beside the Qwen2 model of the same layer sizes and layer count (random
-    weights), through the same step function: tokens per second, and per layer the milliseconds behind them."""
+    """Prefill and decode of a design (``--design filasun|gorulorn``) beside the Qwen2 model of the same layer sizes and as
+    many layers as the design runs (random weights), through the same step function: tokens per second, and the
+    milliseconds behind them."""
     import torch
 
     from litinfer_b200.config import config_from_dict
     from litinfer_b200.models import DecoderModel
 
     layers = args.layers or 6
-    out = {"only": "design", "layers": layers, "prefill_tokens": args.prefill_tokens, "context": args.context, "rows": []}
+    design = getattr(args, "design", "filasun")
+    out = {"only": "design", "design": design, "layers": layers, "prefill_tokens": args.prefill_tokens, "context": args.context, "rows": []}
     for shape in args.design_shapes.split(","):
-        for arch in ("filasun", "qwen2"):
+        runs = layers
+        for arch in (design, "qwen2"):
             if arch == "filasun":
                 cfg = filasun_config(shape, layers)
+            elif arch == "gorulorn":
+                cfg = gorulorn_config(shape, layers)
+                runs = design_layer_runs(cfg)
             else:
                 cfg = bench_config(shape)
-                cfg["num_hidden_layers"] = layers
+                cfg["num_hidden_layers"] = runs
             model = DecoderModel.from_random(config_from_dict(cfg).to_model_spec(), 0, "bfloat16", "cuda:0")
-            row = {"shape": shape, "arch": arch, "weights_gb": round(weight_bytes(model) / 1e9, 3)}
+            row = {"shape": shape, "arch": arch, "layer_runs": runs, "weights_gb": round(weight_bytes(model) / 1e9, 3)}
             ms = time_prefill(model, args.prefill_tokens)
             row["prefill_ms"] = round(ms, 3)
             row["prefill_tok_s"] = round(args.prefill_tokens / ms * 1e3)
@@ -716,7 +749,8 @@ def main() -> int:
                          "a portion of --prefill-tokens prompt tokens")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (so that a profiler lists them)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
-    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "filasun"],
+    ap.add_argument("--design", default="filasun", choices=["filasun", "gorulorn"], help="--only design: the design that runs beside Qwen2")
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "filasun", "gorulorn"],
                     help="which design the parts behind --only are measured on, with the layer sizes of --shape (default: the headline's Qwen2)")
     ap.add_argument("--design-shapes", default="1.5b,7b", help="--only design: the shapes whose layer sizes are run, with commas")
     args = ap.parse_args()
@@ -751,6 +785,13 @@ def main() -> int:
             return 2
         cfg = filasun_config(args.shape, args.layers or 6)
         cfg["num_hidden_layers"], cfg["max_position_embeddings"] = len(cfg["layers"]), cfg["max_positions"]
+        cfg.update(num_key_value_heads=0, head_dim=0, hidden_size=cfg["width"])
+    if args.arch == "gorulorn":
+        if args.only == "all":
+            print("bench.py: --arch gorulorn goes with --only decode|prefill|kernels-decode|kernels-prefill|design")
+            return 2
+        cfg = gorulorn_config(args.shape, args.layers or 6)
+        cfg["num_hidden_layers"], cfg["max_position_embeddings"] = design_layer_runs(cfg), cfg["max_positions"]
         cfg.update(num_key_value_heads=0, head_dim=0, hidden_size=cfg["width"])
     if args.only in ("decode", "kernels-decode") and args.context + 4096 > cfg["max_position_embeddings"]:
         # a longer context than the shape's own limit, on request: the measurement's model allows it

@@ -21,12 +21,12 @@ bool li_attention_decode_accepts(int nh, int nkv, int dh, int page_size);
 int li_attention_decode(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                         const int* ctx_lens, const int* old_lens, const int* q_start, int S, int nh, int nkv, int dh, int page_size, int num_pages,
                         float scale, int window, int max_ctx_len, int expected, float softcap, const float* slopes, const void* gate,
-                        cudaStream_t stream);
+                        int keep_first, const float* sinks, cudaStream_t stream);
 bool li_attention_prefill_accepts(int nh, int nkv, int dh, int page_size);
 int li_attention_prefill(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size,
                          int num_pages, float scale, int window, int max_q_len, int skip_single, float softcap, const float* slopes,
-                         const void* gate, cudaStream_t stream);
+                         const void* gate, int keep_first, const float* sinks, cudaStream_t stream);
 
 bool li_attention_tcgen05_accepts(const void* qkv, const void* kcache, const void* vcache, int nh, int nkv, int dh, int page_size);
 int li_attention_tcgen05(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
@@ -47,12 +47,12 @@ static int validate(int T, int S, int nh, int nkv, int dh, int page_size, int wi
 static int attention_portions(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                               const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
                               float scale, int window, int max_q_len, int max_ctx_len, const int* old_lens, int singles, const int* units,
-                              int slots_portions, int slots_all, float softcap, const float* slopes, const void* gate, bool* done,
-                              cudaStream_t stream) {
+                              int slots_portions, int slots_all, float softcap, const float* slopes, const void* gate, int keep_first,
+                              const float* sinks, bool* done, cudaStream_t stream) {
     *done = false;
-    // changed scores or outputs (a cap, a distance penalty, a gate per head): the mma.sync tiles and the decode kernel take
-    // them, the tcgen05 tiles do not
-    const bool changed = softcap > 0.0f || slopes != nullptr || gate != nullptr;
+    // changed scores or outputs (a cap, a distance penalty, a gate per head, kept first keys behind the window, a sink in
+    // the denominator): the mma.sync tiles and the decode kernel take them, the tcgen05 tiles do not
+    const bool changed = softcap > 0.0f || slopes != nullptr || gate != nullptr || keep_first > 0 || sinks != nullptr;
     const bool tc = !changed && max_q_len >= 64 && scale > 0.0f && li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size);
     if (!tc && scale <= 0.0f) return 0;
     if (!tc && !li_attention_prefill_accepts(nh, nkv, dh, page_size)) return 0;
@@ -62,14 +62,14 @@ static int attention_portions(const void* qkv, void* out, const void* kcache, co
     const int expected = singles > 0 ? singles : (S + 1) / 2;
     if (split)
         if (int rc = li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, dh,
-                                         page_size, num_pages, scale, window, max_ctx_len, expected, softcap, slopes, gate, stream))
+                                         page_size, num_pages, scale, window, max_ctx_len, expected, softcap, slopes, gate, keep_first, sinks, stream))
             return rc;
     *done = true;
     if (tc)
         return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
                                     num_pages, scale, window, max_q_len, split, units, split ? slots_portions : slots_all, stream);
     return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
-                                num_pages, scale, window, max_q_len, split, softcap, slopes, gate, stream);
+                                num_pages, scale, window, max_q_len, split, softcap, slopes, gate, keep_first, sinks, stream);
 }
 
 // singles: how many sequences of the step have one token beside longer ones (0: none; negative: not known, there may be).
@@ -85,16 +85,14 @@ LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache,
     if (T == 0) return 0;
     LI_REQUIRE(keep_first >= 0, "attention: bad keep_first %d", keep_first);
     if (window <= 0) keep_first = 0;                    // without a window every key is seen anyway
-    // kept first keys and sinks: the general kernel has them; the tensor-core kernels do not
-    const bool plain = keep_first == 0 && sinks == nullptr;
-    if (dtype == LI_BF16 && plain) {
+    if (dtype == LI_BF16) {
         if (max_q_len == 1 && T == S && li_attention_decode_accepts(nh, nkv, dh, page_size))
             return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, nullptr, S, nh, nkv, dh, page_size,
-                                       num_pages, scale, window, max_ctx_len, S, softcap, slopes, gate, stream);
+                                       num_pages, scale, window, max_ctx_len, S, softcap, slopes, gate, keep_first, sinks, stream);
         bool done = false;
         const int rc = attention_portions(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
                                           num_pages, scale, window, max_q_len, max_ctx_len, old_lens, singles, units, slots_portions, slots_all,
-                                          softcap, slopes, gate, &done, stream);
+                                          softcap, slopes, gate, keep_first, sinks, &done, stream);
         if (rc || done) return rc;
     }
     return li_attention_generic(qkv, out, kcache, vcache, dtype, block_table, max_blocks, seq_of_token, positions, T, nh, nkv, dh,
@@ -119,14 +117,14 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
     if (which == 0)
         return li_attention_generic(qkv, out, kcache, vcache, dtype, block_table, max_blocks, seq_of_token, positions, T, nh, nkv,
                                     dh, page_size, num_pages, scale, window, softcap, slopes, gate, keep_first, sinks, stream);
-    LI_REQUIRE(keep_first == 0 && sinks == nullptr, "attention: implementation %d takes no kept first keys and no sinks", which);
-    LI_REQUIRE(which != 3 || (softcap <= 0.0f && slopes == nullptr && gate == nullptr), "attention: the tcgen05 kernel takes no cap, slopes or gate");
+    LI_REQUIRE(which != 3 || (softcap <= 0.0f && slopes == nullptr && gate == nullptr && keep_first == 0 && sinks == nullptr),
+               "attention: the tcgen05 kernel takes no cap, slopes, gate, kept first keys or sinks");
     LI_REQUIRE(dtype == LI_BF16, "attention: implementation %d takes bfloat16 only", which);
     if (which == 1) {
         LI_REQUIRE(max_q_len == 1 && T == S, "attention: the decode kernel takes one token per sequence");
         LI_REQUIRE(li_attention_decode_accepts(nh, nkv, dh, page_size), "attention: the decode kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
         return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, nullptr, S, nh, nkv, dh, page_size, num_pages,
-                                   scale, window, max_ctx_len, S, softcap, slopes, gate, stream);
+                                   scale, window, max_ctx_len, S, softcap, slopes, gate, keep_first, sinks, stream);
     }
     if (which == 2 || which == 3) {
         if (which == 2) {
@@ -137,12 +135,11 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
         const int split = (singles != 0 && max_q_len > 1 && li_attention_decode_accepts(nh, nkv, dh, page_size)) ? 1 : 0;
         if (split)
             if (int rc = li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, dh,
-                                             page_size, num_pages, scale, window, max_ctx_len, singles > 0 ? singles : (S + 1) / 2, softcap, slopes,
-                                             gate, stream))
+                                             page_size, num_pages, scale, window, max_ctx_len, singles > 0 ? singles : (S + 1) / 2, softcap, slopes, gate, keep_first, sinks, stream))
                 return rc;
         if (which == 2)
             return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
-                                        num_pages, scale, window, max_q_len, split, softcap, slopes, gate, stream);
+                                        num_pages, scale, window, max_q_len, split, softcap, slopes, gate, keep_first, sinks, stream);
         return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
                                     num_pages, scale, window, max_q_len, split, units, split ? slots_portions : slots_all, stream);
     }

@@ -108,6 +108,16 @@ decode_attention_whole_kernel(const bf16* __restrict__ qkv, const bf16* __restri
 #pragma unroll 1
     for (int b = b_first + warp; b <= b_last; b += WARPS)
         block_step<DH, KB, kMod>(st, qa, kcache, vcache, bt, b * KB, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t, rm);
+    if constexpr (kMod) {
+        // the kept first keys that lie behind the window
+        const int kept_end = window > 0 ? min(mod.keep_first, lo) : 0;
+        if (kept_end > 0) {
+            const int lok[2] = {0, 0}, hik[2] = {kept_end - 1, kept_end - 1};
+#pragma unroll 1
+            for (int key0 = warp * KB; key0 < kept_end; key0 += WARPS * KB)
+                block_step<DH, KB, kMod>(st, qa, kcache, vcache, bt, key0, kvh, nkv, page_size, num_pages, lok, hik, scale, g, t, rm);
+        }
+    }
     const float m0 = st.m[0], m1 = st.m[1];
     const float l0 = quad_sum(st.l[0]), l1 = quad_sum(st.l[1]);
     float* sm_m = sm;
@@ -135,6 +145,12 @@ decode_attention_whole_kernel(const bf16* __restrict__ qkv, const bf16* __restri
         float M = sm_m[r];
 #pragma unroll
         for (int w = 1; w < WARPS; ++w) M = fmaxf(M, sm_m[w * 16 + r]);
+        float sink = -INFINITY;
+        if constexpr (kMod)
+            if (mod.sinks) {
+                sink = mod.sinks[kvh * G + r];
+                M = fmaxf(M, sink);
+            }
         float O = 0.0f, L = 0.0f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
@@ -142,6 +158,7 @@ decode_attention_whole_kernel(const bf16* __restrict__ qkv, const bf16* __restri
             O += sm_o[((size_t)w * G + r) * DH + d] * f;
             L += sm_l[w * 16 + r] * f;
         }
+        if (sink != -INFINITY) L += expf(sink - M);            // the sink joins the denominator once
         float res = L > 0.0f ? O / L : 0.0f;
         if constexpr (kMod)
             if (mod.gate) res *= sigmoid_of(mod.gate[(size_t)tok * nh + kvh * G + r]);
@@ -262,11 +279,13 @@ bool li_attention_decode_accepts(int nh, int nkv, int dh, int page_size) {
 int li_attention_decode(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                         const int* ctx_lens, const int* old_lens, const int* q_start, int S, int nh, int nkv, int dh, int page_size, int num_pages,
                         float scale, int window, int max_ctx_len, int expected, float softcap, const float* slopes, const void* gate,
-                        cudaStream_t stream) {
+                        int keep_first, const float* sinks, cudaStream_t stream) {
     ScoreMod mod;
     mod.softcap = softcap;
     mod.slopes = slopes;
     mod.gate = (const bf16*)gate;
+    mod.keep_first = window > 0 ? keep_first : 0;
+    mod.sinks = sinks;
 #define LI_CASE(D)                                                                                                             \
     case D:                                                                                                                    \
         return mod.any() ? launch<D, true>(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, page_size, \

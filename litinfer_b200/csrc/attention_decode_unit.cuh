@@ -146,6 +146,16 @@ __device__ __forceinline__ void decode_attention_unit(int split, int kvh, int s,
                 block_step<DH, KB, kMod>(st, qa, kcache, vcache, bt, key0, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t, rm);
         }
     }
+    if constexpr (kMod) {
+        // the kept first keys that lie behind the window: the unit that holds the newest key takes them too
+        const int kept_end = (window > 0 && mod.keep_first < lo) ? mod.keep_first : (window > 0 ? lo : 0);
+        if (mod.keep_first > 0 && kept_end > 0 && k_end == ctx) {
+            const int lok[2] = {0, 0}, hik[2] = {kept_end - 1, kept_end - 1};
+#pragma unroll 1
+            for (int key0 = warp * KB; key0 < kept_end; key0 += kWarps * KB)
+                block_step<DH, KB, kMod>(st, qa, kcache, vcache, bt, key0, kvh, nkv, page_size, num_pages, lok, hik, scale, g, t, rm);
+        }
+    }
     const float m0 = st.m[0], m1 = st.m[1];
     const float l0 = quad_sum(st.l[0]), l1 = quad_sum(st.l[1]);
     auto& o = st.o;
@@ -216,6 +226,12 @@ __device__ __forceinline__ void decode_attention_unit(int split, int kvh, int s,
         float M = -INFINITY;
         for (int sp = first + lane; sp <= last; sp += 32) M = fmaxf(M, __ldcg(base + (size_t)sp * (DH + 2) + DH));
         M = warp_max(M);
+        float sink = -INFINITY;
+        if constexpr (kMod)
+            if (mod.sinks) {
+                sink = mod.sinks[kvh * G + r];
+                M = fmaxf(M, sink);
+            }
         float L = 0.0f;
         for (int sp0 = first; sp0 <= last; sp0 += 32) {        // ascending split order within each lane
             const int sp = sp0 + lane;
@@ -227,6 +243,7 @@ __device__ __forceinline__ void decode_attention_unit(int split, int kvh, int s,
             }
         }
         L = warp_sum(L);
+        if (sink != -INFINITY) L += expf(sink - M);            // the sink joins the denominator once
         if (lane == 0) l_sm[r] = L;
     }
     sync();

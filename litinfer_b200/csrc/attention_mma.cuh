@@ -22,12 +22,16 @@
 namespace attn {
 
 // Optional changes of the scores and of the output (see attention_generic.cu): a cap softcap * tanh(s / softcap) after
-// the scale, slopes[h] * (p - key) taken off, and the head's output times sigmoid(gate[token, h]).  All off when zero.
+// the scale, slopes[h] * (p - key) taken off, and the head's output times sigmoid(gate[token, h]).  And of what is seen
+// and summed: with a window the keys below keep_first stay visible behind it; exp(sinks[h]) joins the denominator of head
+// h once.  All off when zero.
 struct ScoreMod {
     float softcap = 0.0f;
     const float* slopes = nullptr;
     const bf16* gate = nullptr;
-    bool any() const { return softcap > 0.0f || slopes != nullptr || gate != nullptr; }
+    int keep_first = 0;
+    const float* sinks = nullptr;
+    bool any() const { return softcap > 0.0f || slopes != nullptr || gate != nullptr || keep_first > 0 || sinks != nullptr; }
 };
 
 // tanh from the fast exponential and reciprocal (relative error about 1e-6): 1 - 2 / (1 + e^(2x)).

@@ -155,21 +155,31 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, c
     };
 
     const int k_first = (cta_key_lo / kKeys) * kKeys;
-    load_tile(0, k_first);
+    // kept first keys (kMod): the tiles that hold those of them that lie before the window's first tile are walked
+    // first, then the window's; `keep` also joins the mask
+    int keep = 0, kept_end = 0;
+    if constexpr (kMod) {
+        keep = window > 0 ? mod.keep_first : 0;
+        if (keep > 0 && k_first > 0) kept_end = min(k_first, ((keep + kKeys - 1) / kKeys) * kKeys);
+    }
+    auto next_tile = [&](int k0) { return (k0 < kept_end && k0 + kKeys >= kept_end) ? k_first : k0 + kKeys; };
+    const int k_start = kept_end > 0 ? 0 : k_first;
+    load_tile(0, k_start);
     cp_async_commit();
     int stage = 0;
 #pragma unroll 1
-    for (int k0 = k_first; k0 <= cta_p_last; k0 += kKeys, stage ^= 1) {
-        const bool more = k0 + kKeys <= cta_p_last;
+    for (int k0 = k_start; k0 <= cta_p_last; k0 = next_tile(k0), stage ^= 1) {
+        const int k_next = next_tile(k0);
+        const bool more = k_next <= cta_p_last;
         if (more) {
-            load_tile(stage ^ 1, k0 + kKeys);
+            load_tile(stage ^ 1, k_next);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
         }
         __syncthreads();
-        if (warp_active && k0 <= warp_p_last && k0 + kKeys > warp_key_lo) {
+        if (warp_active && k0 <= warp_p_last && (k0 + kKeys > warp_key_lo || k0 < keep)) {
             const unsigned char* ks = smem + (size_t)stage * (kKBytes + kVBytes);
             const unsigned char* vs = ks + kKBytes;
             // scores: 8 tiles of 8 keys
@@ -221,7 +231,7 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, c
                         for (int e = 0; e < 2; ++e) {
                             const int key = k0 + tile_key(tau, 2 * t + e);
                             float& v = sc[tau][2 * r + e];
-                            v = (key >= lo[r] && key <= hi[r]) ? v : -INFINITY;
+                            v = (key <= hi[r] && (key >= lo[r] || key < keep)) ? v : -INFINITY;
                             mx = fmaxf(mx, v);
                         }
                     }
@@ -268,8 +278,20 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, c
         __syncthreads();          // the stage is overwritten by the load the next iteration issues
     }
     if (!warp_active) return;
-    const float l0 = quad_sum(st.l[0]), l1 = quad_sum(st.l[1]);
-    float inv0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, inv1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+    float l0 = quad_sum(st.l[0]), l1 = quad_sum(st.l[1]);
+    float shrink0 = 1.0f, shrink1 = 1.0f;
+    if constexpr (kMod) {
+        if (mod.sinks) {
+            // the sink joins the denominator (the running maximum is in base-2 units here)
+            const float sk = mod.sinks[h] * 1.4426950408889634f;
+            const float mn0 = fmaxf(st.m[0], sk), mn1 = fmaxf(st.m[1], sk);
+            shrink0 = st.m[0] == -INFINITY ? 0.0f : exp2f(st.m[0] - mn0);
+            shrink1 = st.m[1] == -INFINITY ? 0.0f : exp2f(st.m[1] - mn1);
+            l0 = l0 * shrink0 + exp2f(sk - mn0);
+            l1 = l1 * shrink1 + exp2f(sk - mn1);
+        }
+    }
+    float inv0 = l0 > 0.0f ? shrink0 / l0 : 0.0f, inv1 = l1 > 0.0f ? shrink1 / l1 : 0.0f;
     if constexpr (kMod) {
         if (mod.gate) {
             if (r_lo < n) inv0 *= attn::sigmoid_of(mod.gate[(size_t)(tok0 + r_lo) * nh + h]);
@@ -315,12 +337,14 @@ bool li_attention_prefill_accepts(int nh, int nkv, int dh, int page_size) {
 int li_attention_prefill(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size,
                          int num_pages, float scale, int window, int max_q_len, int skip_single, float softcap, const float* slopes,
-                         const void* gate, cudaStream_t stream) {
+                         const void* gate, int keep_first, const float* sinks, cudaStream_t stream) {
     (void)T;
     attn::ScoreMod mod;
     mod.softcap = softcap;
     mod.slopes = slopes;
     mod.gate = (const bf16*)gate;
+    mod.keep_first = window > 0 ? keep_first : 0;
+    mod.sinks = sinks;
     LI_REQUIRE(scale > 0.0f, "attention (prefill): the scale must be positive, got %g", (double)scale);
 #define LI_CASE(D)                                                                                                                  \
     case D:                                                                                                                         \

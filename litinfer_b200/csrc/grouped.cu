@@ -5,8 +5,10 @@
 //       a [M, lda] and of out [M, ldc], all columns alike: the experts of a mixture, tokens sorted by expert;
 //     * columns in groups (row_offsets NULL): every group takes all M rows, its inputs at column g * a_gcol of a and its
 //       outputs at column g * c_gcol of out: a map per head.
-//     CUDA-core tiles of 64 x 64 x 16, float accumulation, each output summed over k in ascending order by one thread: a
-//     row's result does not depend on which rows stand beside it.
+//     float32 (and bfloat16 shapes the other kernel refuses): CUDA-core tiles of 64 x 64 x 16.  bfloat16 with K a
+//     multiple of 8: mma.sync tiles of 64 x 64 x 32 (four warps of 16 rows, operands through shared memory with
+//     16-byte asynchronous copies, two stages).  Either way float accumulation, each output summed over k in ascending
+//     order by one thread: a row's result does not depend on which rows stand beside it.
 //   li_moe_route:   scores = sigmoid(logits), the `top` largest per token (the lower index wins a tie); the scores of the
 //     chosen are the weights as they are, not renormalised.
 //   li_moe_sort:    a stable counting sort of the (token, choice) pairs by expert: offsets per expert, the pair at each
@@ -98,6 +100,109 @@ grouped_linear_kernel(const Tin* __restrict__ A, int lda, int a_gcol, const Tin*
         for (int j = 0; j < TN; ++j) {
             const int n = n0 + tx * TN + j;
             if (n < N) c[(size_t)m * ldc + n] = from_float<Tout>(acc[i][j]);
+        }
+    }
+}
+
+// ---- the same on the tensor cores (bfloat16) ----------------------------------------------------------------------------
+
+constexpr int MK = 32, MPAD = 8;          // k elements a stage; padding of a shared row (its 80 bytes keep 16-byte alignment)
+
+__device__ __forceinline__ void cp16(void* dst, const void* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;                               // 0: the destination is filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes));
+}
+
+__device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128)
+grouped_mma_kernel(const bf16* __restrict__ A, int lda, int a_gcol, const bf16* __restrict__ W, bf16* __restrict__ C, int ldc, int c_gcol,
+                   const int* __restrict__ row_offsets, int M, int N, int K, int G) {
+    __shared__ __align__(16) bf16 As[2][BM][MK + MPAD];
+    __shared__ __align__(16) bf16 Ws[2][BN][MK + MPAD];
+    pdl_launch_dependents();
+    pdl_wait();
+    int g, m0, m_end;
+    if (row_offsets) {
+        int tile = blockIdx.y;
+        g = 0;
+        while (g < G) {
+            const int rows = row_offsets[g + 1] - row_offsets[g];
+            const int tiles = (rows + BM - 1) / BM;
+            if (tile < tiles) break;
+            tile -= tiles;
+            ++g;
+        }
+        if (g >= G) return;
+        m0 = row_offsets[g] + tile * BM;
+        m_end = row_offsets[g + 1];
+    } else {
+        g = blockIdx.z;
+        m0 = blockIdx.y * BM;
+        m_end = M;
+    }
+    const bf16* a = A + (size_t)g * a_gcol;
+    const bf16* w = W + (size_t)g * N * K;
+    bf16* c = C + (size_t)g * c_gcol;
+    const int n0 = blockIdx.x * BN;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gq = lane >> 2, t = lane & 3;
+    auto load = [&](int stage, int k0) {
+        // 64 rows of 4 chunks of 8 elements for each operand: 256 chunks each, two per thread
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int idx = tid + i * 128;
+            const int r = idx >> 2, ch = idx & 3;
+            const int k = k0 + ch * 8;
+            const bool ka = k < K;
+            const bool va = ka && m0 + r < m_end, vw = ka && n0 + r < N;
+            cp16(&As[stage][r][ch * 8], va ? a + (size_t)(m0 + r) * lda + k : a, va);
+            cp16(&Ws[stage][r][ch * 8], vw ? w + (size_t)(n0 + r) * K + k : w, vw);
+        }
+        asm volatile("cp.async.commit_group;");
+    };
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+    load(0, 0);
+    int stage = 0;
+    for (int k0 = 0; k0 < K; k0 += MK, stage ^= 1) {
+        if (k0 + MK < K) {
+            load(stage ^ 1, k0 + MK);
+            asm volatile("cp.async.wait_group 1;");
+        } else {
+            asm volatile("cp.async.wait_group 0;");
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < MK; ks += 16) {
+            const bf16* ar = &As[stage][warp * 16 + gq][ks + 2 * t];
+            const unsigned a0 = *reinterpret_cast<const unsigned*>(ar), a1 = *reinterpret_cast<const unsigned*>(ar + 8 * (MK + MPAD));
+            const unsigned a2 = *reinterpret_cast<const unsigned*>(ar + 8), a3 = *reinterpret_cast<const unsigned*>(ar + 8 * (MK + MPAD) + 8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bf16* wr = &Ws[stage][j * 8 + gq][ks + 2 * t];
+                mma16816(acc[j], a0, a1, a2, a3, *reinterpret_cast<const unsigned*>(wr), *reinterpret_cast<const unsigned*>(wr + 8));
+            }
+        }
+        __syncthreads();                     // the stage is overwritten by the load the next iteration issues
+    }
+    const int r_lo = m0 + warp * 16 + gq, r_hi = r_lo + 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int n = n0 + j * 8 + 2 * t;
+        if (n < N) {
+            if (r_lo < m_end) c[(size_t)r_lo * ldc + n] = __float2bfloat16_rn(acc[j][0]);
+            if (r_hi < m_end) c[(size_t)r_hi * ldc + n] = __float2bfloat16_rn(acc[j][2]);
+        }
+        if (n + 1 < N) {
+            if (r_lo < m_end) c[(size_t)r_lo * ldc + n + 1] = __float2bfloat16_rn(acc[j][1]);
+            if (r_hi < m_end) c[(size_t)r_hi * ldc + n + 1] = __float2bfloat16_rn(acc[j][3]);
         }
     }
 }
@@ -236,7 +341,12 @@ LI_EXPORT int li_grouped_linear(const void* a, int lda, int a_gcol, const void* 
     const dim3 grid(ceil_div(N, BN), row_offsets ? row_tiles + G : row_tiles, row_offsets ? 1 : G);
     LI_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "grouped_linear: too many tiles for one launch");
     cudaError_t e;
-    if (dtype == LI_F32)
+    // 16-byte copies: every row and every group's first column on a 16-byte boundary
+    const bool aligned = K % 8 == 0 && lda % 8 == 0 && a_gcol % 8 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0;
+    if (dtype == LI_BF16 && aligned)
+        e = li_launch_pdl(grouped_mma_kernel, grid, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w, (bf16*)out, ldc, c_gcol,
+                          row_offsets, M, N, K, G);
+    else if (dtype == LI_F32)
         e = li_launch_pdl(grouped_linear_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)a, lda, a_gcol, (const float*)w, (float*)out,
                           ldc, c_gcol, row_offsets, M, N, K, G);
     else
