@@ -172,7 +172,8 @@ template <int BM, int BN, typename Tout, int kSwiglu, bool kPair = false, bool k
 __global__ void __launch_bounds__(threads_of<kRope>(), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, Tout* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag,
-                    float* __restrict__ partial, unsigned* __restrict__ counters, int ksplit, const RopeEpilogue rope) {
+                    float* __restrict__ partial, unsigned* __restrict__ counters, int ksplit, const RopeEpilogue rope,
+                    const int* __restrict__ tile_group) {
     extern __shared__ unsigned char smem_raw[];
     using SS = SharedStorage<BM, BN, kPair>;
     constexpr int kStages = Tile<BM, BN, kPair>::kStages;
@@ -185,6 +186,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // take consecutive tiles of rows
     const int m0 = kPair ? ((int)blockIdx.y * 2 + (int)(blockIdx.x & 1)) * BM : (int)blockIdx.y * BM;
     const int n0 = kPair ? (int)(blockIdx.x >> 1) * BN : (int)blockIdx.x * BN;
+    // Products in groups (tile_group, single CTAs only): the groups' matrices are stacked along the rows of w, every tile
+    // of rows multiplies with the matrix of its own group, and a tile that belongs to no group (-1) has nothing to do.
+    // The table is made by the kernel before this one, so nothing is asked for before that kernel has finished.
+    int wn0 = n0;
+    if constexpr (!kPair) {
+        if (tile_group != nullptr) {
+            pdl_wait();
+            const int group = tile_group[blockIdx.y];
+            if (group < 0) return;
+            wn0 = n0 + group * N;
+        }
+    }
     const int nkb_total = (K + BK - 1) / BK;
     const int split = blockIdx.z;
     const int kb_first = (int)((long long)split * nkb_total / ksplit);
@@ -241,7 +254,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tma_load_2d_pair(sm.b[kb], &map_w, (kb_first + kb) * BK, n0 + (int)pair_rank * (BN / 2), &sm.full[kb]);
                 } else {
                     mbar_expect_tx(&sm.full[kb], kStageBytesA + kStageBytesB);
-                    tma_load_2d(sm.b[kb], &map_w, (kb_first + kb) * BK, n0, &sm.full[kb]);
+                    tma_load_2d(sm.b[kb], &map_w, (kb_first + kb) * BK, wn0, &sm.full[kb]);
                 }
             }
             pdl_wait();
@@ -263,7 +276,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 } else {
                     mbar_expect_tx(&sm.full[s], kStageBytesA + kStageBytesB);
                     tma_load_2d(sm.a[s], &map_a, (kb_first + kb) * BK, m0, &sm.full[s]);
-                    tma_load_2d(sm.b[s], &map_w, (kb_first + kb) * BK, n0, &sm.full[s]);
+                    tma_load_2d(sm.b[s], &map_w, (kb_first + kb) * BK, wn0, &sm.full[s]);
                 }
                 issued = kb + 1;
             }
@@ -452,7 +465,7 @@ int split_workspace(size_t floats, SplitWorkspace** out) {
 
 template <int BM, int BN, typename Tout, int kSwiglu, bool kPair = false, bool kRope = false>
 int launch_tile(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, int ksplit = 1,
-                const RopeEpilogue& rope = RopeEpilogue{}) {
+                const RopeEpilogue& rope = RopeEpilogue{}, const int* tile_group = nullptr, int groups = 1) {
     EncodeTiledFn encode = nullptr;
     int *g_error_host = nullptr, *g_error_dev = nullptr;
     if (int rc = setup(&encode, &g_error_host, &g_error_dev)) return rc;
@@ -460,7 +473,7 @@ int launch_tile(const void* a, const void* w, const float* bias, void* out, int 
         return li_fail("linear (tcgen05): an earlier launch gave up waiting on a barrier (status %d); the results since then are invalid", *g_error_host);
     CUtensorMap map_a, map_w;
     if (int rc = make_map(&map_a, a, M, K, BM)) return rc;
-    if (int rc = make_map(&map_w, w, N, K, Tile<BM, BN, kPair>::kRowsB)) return rc;
+    if (int rc = make_map(&map_w, w, N * groups, K, Tile<BM, BN, kPair>::kRowsB)) return rc;       // (groups: their matrices one below the other)
     const size_t smem = sizeof(SharedStorage<BM, BN, kPair>) + 1024;
     static bool raised = false;
     if (!raised) {
@@ -480,7 +493,7 @@ int launch_tile(const void* a, const void* w, const float* bias, void* out, int 
         if (int rc = split_workspace((size_t)ksplit * grid.x * grid.y * BM * BN, &ws)) return rc;
     }
     li_launch_pdl(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu, kPair, kRope>, grid, dim3(threads_of<kRope>()), smem, stream, dim3(kPair ? 2 : 1, 1, 1), map_a, map_w,
-                  bias, (Tout*)out, M, N, K, g_error_dev, ws->partial, ws->counters, ksplit, rope);
+                  bias, (Tout*)out, M, N, K, g_error_dev, ws->partial, ws->counters, ksplit, rope, tile_group);
     return li_check_launch("linear (tcgen05)");
 }
 
@@ -594,6 +607,14 @@ int li_linear_tcgen05_rope(const void* a, const void* w, const float* bias, void
                "linear + rope (tcgen05): N=%d does not match %d + 2 x %d heads of 128, or a null operand", N, rope.nh, rope.nkv);
     if (pair_tiles_chosen(M, N, K)) return launch_tile<128, 256, bf16, false, true, true>(a, w, bias, out, M, N, K, stream, 1, rope);
     return launch_tile<128, 128, bf16, false, false, true>(a, w, bias, out, M, N, K, stream, 1, rope);
+}
+
+// Products in groups: a [M, K] with M a multiple of 128, every tile of 128 rows the rows of one group (tile_group[tile], -1: none);
+// w [G, N, K]; out [M, N] in bfloat16.  Tiles of 128 x 128, one CTA each.
+int li_linear_tcgen05_grouped(const void* a, const void* w, void* out, int M, int N, int K, int G, const int* tile_group, cudaStream_t stream) {
+    LI_REQUIRE(M % 128 == 0 && G >= 1 && tile_group != nullptr, "grouped linear (tcgen05): rows %d must be whole tiles of 128 with a table of their groups", M);
+    LI_REQUIRE(K >= 8 && K % 8 == 0 && ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0), "grouped linear (tcgen05): refuses K=%d or unaligned operands", K);
+    return launch_tile<128, 128, bf16, 0>(a, w, nullptr, out, M, N, K, stream, 1, RopeEpilogue{}, tile_group, G);
 }
 
 // 0: tile size by shape; 1: 128 x 128 always; 2: 256 x 256 always, one CTA a tile; 3: 256 x 128 always; 4: pairs of CTAs on

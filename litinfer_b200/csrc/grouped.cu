@@ -6,8 +6,9 @@
 //     * columns in groups (row_offsets NULL): every group takes all M rows, its inputs at column g * a_gcol of a and its
 //       outputs at column g * c_gcol of out: a map per head.
 //     float32 (and bfloat16 shapes the other kernel refuses): CUDA-core tiles of 64 x 64 x 16.  bfloat16 with K a
-//     multiple of 8: mma.sync tiles of 64 x 64 x 32 (four warps of 16 rows, operands through shared memory with
-//     16-byte asynchronous copies, two stages).  Either way float accumulation, each output summed over k in ascending
+//     multiple of 8: mma.sync tiles of 64 x 64 (many rows a group) or 16 x 64 (few: the weights are what is read; four
+//     stages), operands through shared memory with 16-byte asynchronous copies; rows in groups whose runs are padded to
+//     128 rows and number 256 or more go to tcgen05 tiles (gemm_tcgen05.cu).  Either way float accumulation, each output summed over k in ascending
 //     order by one thread: a row's result does not depend on which rows stand beside it.
 //   li_moe_route:   scores = sigmoid(logits), the `top` largest per token (the lower index wins a tie); the scores of the
 //     chosen are the weights as they are, not renormalised.
@@ -106,7 +107,7 @@ grouped_linear_kernel(const Tin* __restrict__ A, int lda, int a_gcol, const Tin*
 
 // ---- the same on the tensor cores (bfloat16) ----------------------------------------------------------------------------
 
-constexpr int MK = 32, MPAD = 8;          // k elements a stage; padding of a shared row (its 80 bytes keep 16-byte alignment)
+constexpr int MPAD = 8;                   // padding of a shared row: rows of TK + 8 elements keep 16-byte alignment and spread over the banks
 
 __device__ __forceinline__ void cp16(void* dst, const void* src, bool valid) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -120,11 +121,16 @@ __device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// A tile of TM rows x 64 columns a CTA of four warps, TK elements of k a stage, ST stages of 16-byte asynchronous copies.
+// TM 64: many rows a group (portions of prompts); a warp takes 16 rows and all 64 columns.  TM 16: few rows a group
+// (single tokens: the weights are what is read): a warp takes all 16 rows and 16 of the columns, and four stages of
+// 64 elements keep more of the weights on their way.
+template <int TM, int TK, int ST>
 __global__ void __launch_bounds__(128)
 grouped_mma_kernel(const bf16* __restrict__ A, int lda, int a_gcol, const bf16* __restrict__ W, bf16* __restrict__ C, int ldc, int c_gcol,
                    const int* __restrict__ row_offsets, int M, int N, int K, int G) {
-    __shared__ __align__(16) bf16 As[2][BM][MK + MPAD];
-    __shared__ __align__(16) bf16 Ws[2][BN][MK + MPAD];
+    __shared__ __align__(16) bf16 As[ST][TM][TK + MPAD];
+    __shared__ __align__(16) bf16 Ws[ST][BN][TK + MPAD];
     pdl_launch_dependents();
     pdl_wait();
     int g, m0, m_end;
@@ -133,17 +139,17 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, int a_gcol, const bf16* 
         g = 0;
         while (g < G) {
             const int rows = row_offsets[g + 1] - row_offsets[g];
-            const int tiles = (rows + BM - 1) / BM;
+            const int tiles = (rows + TM - 1) / TM;
             if (tile < tiles) break;
             tile -= tiles;
             ++g;
         }
         if (g >= G) return;
-        m0 = row_offsets[g] + tile * BM;
+        m0 = row_offsets[g] + tile * TM;
         m_end = row_offsets[g + 1];
     } else {
         g = blockIdx.z;
-        m0 = blockIdx.y * BM;
+        m0 = blockIdx.y * TM;
         m_end = M;
     }
     const bf16* a = A + (size_t)g * a_gcol;
@@ -152,50 +158,54 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, int a_gcol, const bf16* 
     const int n0 = blockIdx.x * BN;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gq = lane >> 2, t = lane & 3;
+    constexpr int CH = TK / 8;                                      // 16-byte chunks of a row of a stage
     auto load = [&](int stage, int k0) {
-        // 64 rows of 4 chunks of 8 elements for each operand: 256 chunks each, two per thread
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int idx = tid + i * 128;
-            const int r = idx >> 2, ch = idx & 3;
+        for (int idx = tid; idx < TM * CH; idx += 128) {
+            const int r = idx / CH, ch = idx - r * CH;
             const int k = k0 + ch * 8;
-            const bool ka = k < K;
-            const bool va = ka && m0 + r < m_end, vw = ka && n0 + r < N;
-            cp16(&As[stage][r][ch * 8], va ? a + (size_t)(m0 + r) * lda + k : a, va);
-            cp16(&Ws[stage][r][ch * 8], vw ? w + (size_t)(n0 + r) * K + k : w, vw);
+            const bool v = k < K && m0 + r < m_end;
+            cp16(&As[stage][r][ch * 8], v ? a + (size_t)(m0 + r) * lda + k : a, v);
         }
-        asm volatile("cp.async.commit_group;");
+        for (int idx = tid; idx < BN * CH; idx += 128) {
+            const int r = idx / CH, ch = idx - r * CH;
+            const int k = k0 + ch * 8;
+            const bool v = k < K && n0 + r < N;
+            cp16(&Ws[stage][r][ch * 8], v ? w + (size_t)(n0 + r) * K + k : w, v);
+        }
     };
-    float acc[8][4];
+    constexpr int NT = TM == 64 ? 8 : 2;                            // tiles of 8 columns a warp
+    const int row0 = TM == 64 ? warp * 16 : 0, col0 = TM == 64 ? 0 : warp * 16;
+    float acc[NT][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
-    load(0, 0);
-    int stage = 0;
-    for (int k0 = 0; k0 < K; k0 += MK, stage ^= 1) {
-        if (k0 + MK < K) {
-            load(stage ^ 1, k0 + MK);
-            asm volatile("cp.async.wait_group 1;");
-        } else {
-            asm volatile("cp.async.wait_group 0;");
-        }
-        __syncthreads();
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+    const int nk = (K + TK - 1) / TK;
 #pragma unroll
-        for (int ks = 0; ks < MK; ks += 16) {
-            const bf16* ar = &As[stage][warp * 16 + gq][ks + 2 * t];
-            const unsigned a0 = *reinterpret_cast<const unsigned*>(ar), a1 = *reinterpret_cast<const unsigned*>(ar + 8 * (MK + MPAD));
-            const unsigned a2 = *reinterpret_cast<const unsigned*>(ar + 8), a3 = *reinterpret_cast<const unsigned*>(ar + 8 * (MK + MPAD) + 8);
+    for (int s = 0; s < ST - 1; ++s) {
+        if (s < nk) load(s, s * TK);
+        asm volatile("cp.async.commit_group;");
+    }
+    for (int kb = 0; kb < nk; ++kb) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(ST - 2));
+        __syncthreads();                     // stage kb has landed for everybody, and everybody is done with the stage that is loaded next
+        if (kb + ST - 1 < nk) load((kb + ST - 1) % ST, (kb + ST - 1) * TK);
+        asm volatile("cp.async.commit_group;");
+        const int stage = kb % ST;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const bf16* wr = &Ws[stage][j * 8 + gq][ks + 2 * t];
+        for (int ks = 0; ks < TK; ks += 16) {
+            const bf16* ar = &As[stage][row0 + gq][ks + 2 * t];
+            const unsigned a0 = *reinterpret_cast<const unsigned*>(ar), a1 = *reinterpret_cast<const unsigned*>(ar + 8 * (TK + MPAD));
+            const unsigned a2 = *reinterpret_cast<const unsigned*>(ar + 8), a3 = *reinterpret_cast<const unsigned*>(ar + 8 * (TK + MPAD) + 8);
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const bf16* wr = &Ws[stage][col0 + j * 8 + gq][ks + 2 * t];
                 mma16816(acc[j], a0, a1, a2, a3, *reinterpret_cast<const unsigned*>(wr), *reinterpret_cast<const unsigned*>(wr + 8));
             }
         }
-        __syncthreads();                     // the stage is overwritten by the load the next iteration issues
     }
-    const int r_lo = m0 + warp * 16 + gq, r_hi = r_lo + 8;
+    const int r_lo = m0 + row0 + gq, r_hi = r_lo + 8;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int n = n0 + j * 8 + 2 * t;
+    for (int j = 0; j < NT; ++j) {
+        const int n = n0 + col0 + j * 8 + 2 * t;
         if (n < N) {
             if (r_lo < m_end) c[(size_t)r_lo * ldc + n] = __float2bfloat16_rn(acc[j][0]);
             if (r_hi < m_end) c[(size_t)r_hi * ldc + n] = __float2bfloat16_rn(acc[j][2]);
@@ -247,26 +257,31 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
     }
 }
 
-// One block per expert.  n pairs (token, choice) in order; ids[i] is pair i's expert.
-__global__ void moe_sort_kernel(const int* __restrict__ ids, int n, int E, int* __restrict__ offsets, int* __restrict__ pair_at,
-                                int* __restrict__ place_of) {
+// One block per expert.  n pairs (token, choice) in order; ids[i] is pair i's expert.  Every expert's run of rows starts
+// at a multiple of `pad` (1: runs follow one another closely); the places between a run's last pair and the next run
+// hold no pair (-1).  tile_group (may be NULL; pad > 1): for every tile of `pad` rows, the expert it belongs to, -1 behind the last run.
+__global__ void moe_sort_kernel(const int* __restrict__ ids, int n, int E, int pad, int* __restrict__ offsets, int* __restrict__ pair_at,
+                                int* __restrict__ place_of, int* __restrict__ tile_group, int n_tiles, int places) {
     __shared__ int warp_total[32];
-    __shared__ int less_total[32];
+    __shared__ int hist[kMaxExpertsPerLane * 32];
     __shared__ int base_eq;
     pdl_launch_dependents();
     pdl_wait();
     const int e = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    // how many pairs go to experts before this one: where this expert's rows start
-    int less = 0;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) less += ids[i] < e ? 1 : 0;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) less += __shfl_xor_sync(0xffffffffu, less, o);
-    if (lane == 0) less_total[warp] = less;
+    // how many pairs go to every expert (integer sums: the same whatever the order), then where this expert's rows start
+    for (int i = threadIdx.x; i < E; i += blockDim.x) hist[i] = 0;
     if (threadIdx.x == 0) base_eq = 0;
     __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int id = ids[i];
+        if (id >= 0 && id < E) atomicAdd(&hist[id], 1);
+    }
+    __syncthreads();
     int start = 0;
-    for (int w = 0; w < nwarps; ++w) start += less_total[w];
+    for (int x = 0; x < e; ++x) start += (hist[x] + pad - 1) / pad * pad;
+    const int mine_total = hist[e];
+    const int end = start + (mine_total + pad - 1) / pad * pad;
     // this expert's pairs, in order
     for (int base = 0; base < n; base += blockDim.x) {
         const int i = base + threadIdx.x;
@@ -289,9 +304,17 @@ __global__ void moe_sort_kernel(const int* __restrict__ ids, int n, int E, int* 
         }
         __syncthreads();
     }
+    for (int r = start + mine_total + threadIdx.x; r < end; r += blockDim.x) pair_at[r] = -1;
+    if (e == E - 1)
+        for (int r = end + threadIdx.x; r < places; r += blockDim.x) pair_at[r] = -1;          // places behind the last run belong to nobody
+    if (tile_group != nullptr) {
+        for (int tl = start / pad + threadIdx.x; tl < end / pad && tl < n_tiles; tl += blockDim.x) tile_group[tl] = e;
+        if (e == E - 1)
+            for (int tl = end / pad + threadIdx.x; tl < n_tiles; tl += blockDim.x) tile_group[tl] = -1;
+    }
     if (threadIdx.x == 0) {
         offsets[e] = start;
-        if (e == E - 1) offsets[E] = start + base_eq;
+        if (e == E - 1) offsets[E] = end;
     }
 }
 
@@ -302,8 +325,12 @@ __global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict
     pdl_wait();
     const int r = blockIdx.x;
     const int pair = pair_at[r];
-    const T* src = h + (size_t)(pair / top) * H;
     T* dst = out + (size_t)r * H;
+    if (pair < 0) {                                        // a place between two experts' runs: a row of zeros
+        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = from_float<T>(0.0f);
+        return;
+    }
+    const T* src = h + (size_t)(pair / top) * H;
     if (weights) {
         const float w = weights[pair];
         for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = from_float<T>(w * to_float(src[i]));
@@ -330,21 +357,37 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __rest
 
 }  // namespace
 
-LI_EXPORT int li_grouped_linear(const void* a, int lda, int a_gcol, const void* w, void* out, int ldc, int c_gcol, const int* row_offsets, int dtype,
-                                int M, int N, int K, int G, cudaStream_t stream) {
+int li_linear_tcgen05_grouped(const void* a, const void* w, void* out, int M, int N, int K, int G, const int* tile_group, cudaStream_t stream);
+
+// tile_group (may be NULL; rows in groups whose runs start at multiples of 128, li_moe_sort with pad 128): the group of
+// every tile of 128 rows; bfloat16 products of at least kTensorRows rows then run on tcgen05 tiles.
+constexpr int kTensorRows = 256;
+
+LI_EXPORT int li_grouped_linear(const void* a, int lda, int a_gcol, const void* w, void* out, int ldc, int c_gcol, const int* row_offsets,
+                                const int* tile_group, int dtype, int M, int N, int K, int G, cudaStream_t stream) {
     LI_REQUIRE(M >= 0 && N > 0 && K > 0 && G > 0, "grouped_linear: bad sizes M=%d N=%d K=%d G=%d", M, N, K, G);
     LI_REQUIRE(lda >= K && ldc >= N, "grouped_linear: rows of %d and %d elements cannot hold K=%d and N=%d", lda, ldc, K, N);
     LI_REQUIRE(row_offsets == nullptr || (a_gcol == 0 && c_gcol == 0), "grouped_linear: groups are rows or columns, not both");
     LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "grouped_linear: unknown dtype %d", dtype);
     if (M == 0) return 0;
+    if (dtype == LI_BF16 && row_offsets != nullptr && tile_group != nullptr && M >= kTensorRows && M % 128 == 0 && lda == K && ldc == N &&
+        K % 8 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0)
+        return li_linear_tcgen05_grouped(a, w, out, M, N, K, G, tile_group, stream);
     const int row_tiles = ceil_div(M, BM);
     const dim3 grid(ceil_div(N, BN), row_offsets ? row_tiles + G : row_tiles, row_offsets ? 1 : G);
     LI_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "grouped_linear: too many tiles for one launch");
     cudaError_t e;
     // 16-byte copies: every row and every group's first column on a 16-byte boundary
     const bool aligned = K % 8 == 0 && lda % 8 == 0 && a_gcol % 8 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0;
-    if (dtype == LI_BF16 && aligned)
-        e = li_launch_pdl(grouped_mma_kernel, grid, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w, (bf16*)out, ldc, c_gcol,
+    // few rows a group (single tokens): tiles of 16 rows, more of the weights in flight
+    const bool few = row_offsets ? M <= 32 * G : M <= 32;
+    if (dtype == LI_BF16 && aligned && few) {
+        const int tiles16 = ceil_div(M, 16);
+        const dim3 grid16(ceil_div(N, BN), row_offsets ? tiles16 + G : tiles16, row_offsets ? 1 : G);
+        e = li_launch_pdl(grouped_mma_kernel<16, 64, 4>, grid16, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w, (bf16*)out, ldc,
+                          c_gcol, row_offsets, M, N, K, G);
+    } else if (dtype == LI_BF16 && aligned)
+        e = li_launch_pdl(grouped_mma_kernel<64, 32, 3>, grid, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w, (bf16*)out, ldc, c_gcol,
                           row_offsets, M, N, K, G);
     else if (dtype == LI_F32)
         e = li_launch_pdl(grouped_linear_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)a, lda, a_gcol, (const float*)w, (float*)out,
@@ -365,14 +408,19 @@ LI_EXPORT int li_moe_route(const float* logits, int T, int E, int top, int* ids,
     return li_check_launch("moe_route");
 }
 
-LI_EXPORT int li_moe_sort(const int* ids, int n, int E, int* offsets, int* pair_at, int* place_of, cudaStream_t stream) {
-    LI_REQUIRE(n >= 0 && E > 0, "moe_sort: bad sizes");
-    const cudaError_t e = li_launch_pdl(moe_sort_kernel, dim3(E), dim3(256), 0, stream, ids, n, E, offsets, pair_at, place_of);
+// pad: every expert's run of rows starts at a multiple of it; pair_at has `places` entries, room for n + E (pad - 1) of them,
+// and tile_group (may be NULL) one entry for each of its n_tiles tiles of pad rows.
+LI_EXPORT int li_moe_sort(const int* ids, int n, int E, int pad, int* offsets, int* pair_at, int* place_of, int* tile_group, int n_tiles,
+                          int places, cudaStream_t stream) {
+    LI_REQUIRE(n >= 0 && E > 0 && pad >= 1, "moe_sort: bad sizes");
+    LI_REQUIRE(places >= n + (pad > 1 ? E * (pad - 1) : 0), "moe_sort: %d places cannot hold %d pairs in runs padded to %d", places, n, pad);
+    LI_REQUIRE(E <= 32 * kMaxExpertsPerLane, "moe_sort: %d experts are more than %d", E, 32 * kMaxExpertsPerLane);
+    const cudaError_t e = li_launch_pdl(moe_sort_kernel, dim3(E), dim3(256), 0, stream, ids, n, E, pad, offsets, pair_at, place_of, tile_group, n_tiles, places);
     if (e != cudaSuccess) return li_fail("moe_sort: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("moe_sort");
 }
 
-// out [n, H]: row r is h[pair_at[r] / top], times weights[pair_at[r]] if weights is given.
+// out [n, H]: row r is h[pair_at[r] / top], times weights[pair_at[r]] if weights is given; zeros where pair_at[r] < 0.
 LI_EXPORT int li_moe_gather(const void* h, int dtype, const int* pair_at, const float* weights, int n, int top, int H, void* out, cudaStream_t stream) {
     LI_REQUIRE(n >= 0 && top > 0 && H > 0, "moe_gather: bad sizes");
     LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "moe_gather: unknown dtype %d", dtype);

@@ -243,17 +243,21 @@ int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* co
 
 /* ---- grouped.cu: products in groups, routing of a mixture of experts ---- */
 /* out_g = a_g w_g^T, w [G, N, K].  row_offsets [G + 1] (device): group g owns those rows of a [M, lda] and out [M, ldc].
- * row_offsets NULL: every group takes all M rows, inputs at column g * a_gcol, outputs at column g * c_gcol. */
-int li_grouped_linear(const void* a, int lda, int a_gcol, const void* w, void* out, int ldc, int c_gcol, const int* row_offsets, int dtype,
-    int M, int N, int K, int G, cudaStream_t stream);
+ * row_offsets NULL: every group takes all M rows, inputs at column g * a_gcol, outputs at column g * c_gcol.
+ * tile_group (may be NULL): with runs of rows that start at multiples of 128, the group of every tile of 128 rows (-1: none);
+ * large bfloat16 products then run on tcgen05 tiles. */
+int li_grouped_linear(const void* a, int lda, int a_gcol, const void* w, void* out, int ldc, int c_gcol, const int* row_offsets,
+    const int* tile_group, int dtype, int M, int N, int K, int G, cudaStream_t stream);
 
 /* ids, weights [T, top]: the experts with the largest sigmoid(logits [T, E]) and those scores. */
 int li_moe_route(const float* logits, int T, int E, int top, int* ids, float* weights, cudaStream_t stream);
 
-/* Stable sort of n (token, choice) pairs by expert: offsets [E + 1], pair_at [n] (pair at a sorted place), place_of [n]. */
-int li_moe_sort(const int* ids, int n, int E, int* offsets, int* pair_at, int* place_of, cudaStream_t stream);
+/* Stable sort of n (token, choice) pairs by expert: offsets [E + 1], pair_at (pair at a sorted place, -1: none), place_of [n].
+ * Every expert's run starts at a multiple of pad; pair_at has `places` entries; tile_group (may be NULL) [n_tiles]: the expert of every tile of pad rows. */
+int li_moe_sort(const int* ids, int n, int E, int pad, int* offsets, int* pair_at, int* place_of, int* tile_group, int n_tiles,
+    int places, cudaStream_t stream);
 
-/* out [n, H]: row r is h[pair_at[r] / top], times weights[pair_at[r]] if weights is given. */
+/* out [n, H]: row r is h[pair_at[r] / top], times weights[pair_at[r]] if weights is given; zeros where pair_at[r] < 0. */
 int li_moe_gather(const void* h, int dtype, const int* pair_at, const float* weights, int n, int top, int H, void* out, cudaStream_t stream);
 
 /* y [T, H]: y[t] = sum_k rows[place_of[t * top + k]] (times weights[t * top + k] if weights is given). */

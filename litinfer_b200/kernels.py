@@ -849,10 +849,12 @@ def conv_norm_rope_kv(proj: torch.Tensor, out: torch.Tensor, conv_w: Optional[to
 # --------------------------------------------------------------------------
 
 def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_offsets: Optional[torch.Tensor] = None,
-                   a_group_cols: int = 0, out_group_cols: int = 0) -> None:
+                   a_group_cols: int = 0, out_group_cols: int = 0, tile_group: Optional[torch.Tensor] = None) -> None:
     """``weight`` [G, N, K]: a product per group.  With ``row_offsets`` (int32 [G + 1] on the device) group g owns the rows
     ``row_offsets[g] .. row_offsets[g + 1] - 1`` of ``a`` [M, K] and ``out`` [M, N].  Without, every group takes all rows, its
-    inputs at column ``g * a_group_cols`` of ``a`` and its outputs at column ``g * out_group_cols`` of ``out`` (a map per head)."""
+    inputs at column ``g * a_group_cols`` of ``a`` and its outputs at column ``g * out_group_cols`` of ``out`` (a map per head).
+    ``tile_group`` (int32 on the device; from :func:`moe_sort` with ``pad`` 128): the group of every tile of 128 rows when
+    the groups' runs start at multiples of 128; large bfloat16 products then run on the tcgen05 tiles."""
     G, N, Kd = weight.shape
     M = a.shape[0]
     _need(a, "grouped input")
@@ -866,8 +868,12 @@ def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row
             raise KernelError(f"grouped_linear: rows in groups need a [M, {Kd}] and out [M, {N}]")
     elif (G - 1) * a_group_cols + Kd > a.shape[1] or (G - 1) * out_group_cols + N > out.shape[1]:
         raise KernelError("grouped_linear: the groups' columns do not fit the rows")
+    if tile_group is not None:
+        _need(tile_group, "groups of the row tiles", torch.int32)
+        if row_offsets is None or tile_group.numel() * 128 < M:
+            raise KernelError("grouped_linear: a table of the tiles' groups goes with row offsets and covers every tile of 128 rows")
     _check(library().li_grouped_linear(_p(a), _i(a.shape[1]), _i(a_group_cols), _p(weight), _p(out), _i(out.shape[1]), _i(out_group_cols),
-                                       _p(row_offsets), _i(_dt(a)), _i(M), _i(N), _i(Kd), _i(G), _stream(out)), "grouped_linear")
+                                       _p(row_offsets), _p(tile_group), _i(_dt(a)), _i(M), _i(N), _i(Kd), _i(G), _stream(out)), "grouped_linear")
 
 
 def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
@@ -880,23 +886,38 @@ def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.
     _check(library().li_moe_route(_p(logits), _i(T), _i(E), _i(top), _p(ids), _p(weights), _stream(ids)), "moe_route")
 
 
-def moe_sort(ids: torch.Tensor, experts: int, offsets: torch.Tensor, pair_at: torch.Tensor, place_of: torch.Tensor) -> None:
+def sorted_rows(pairs: int, experts: int, pad: int = 1) -> int:
+    """How many places the sorted order of ``pairs`` (token, choice) pairs has when every expert's run starts at a multiple of ``pad``."""
+    return pairs if pad <= 1 else -(-(pairs + experts * (pad - 1)) // pad) * pad
+
+
+def moe_sort(ids: torch.Tensor, experts: int, offsets: torch.Tensor, pair_at: torch.Tensor, place_of: torch.Tensor, pad: int = 1,
+             tile_group: Optional[torch.Tensor] = None) -> None:
     """A stable sort of the (token, choice) pairs by expert: ``offsets`` [experts + 1] (where each expert's rows start),
-    ``pair_at`` [n] (which pair stands at a sorted place), ``place_of`` [n] (the sorted place of a pair)."""
+    ``pair_at`` (which pair stands at a sorted place; -1: none), ``place_of`` [n] (the sorted place of a pair).  ``pad`` > 1:
+    every expert's run starts at a multiple of it, ``pair_at`` has :func:`sorted_rows` places, and ``tile_group`` (if given, one
+    entry per ``pad`` places) says which expert each tile of ``pad`` rows belongs to (-1 behind the last run)."""
     n = ids.numel()
+    R = sorted_rows(n, experts, pad)
     _need(ids, "expert ids", torch.int32)
     _need(offsets, "row offsets", torch.int32, (experts + 1,))
-    _need(pair_at, "pair at place", torch.int32, (n,))
+    _need(pair_at, "pair at place", torch.int32, (R,))
     _need(place_of, "place of pair", torch.int32, (n,))
-    _check(library().li_moe_sort(_p(ids), _i(n), _i(experts), _p(offsets), _p(pair_at), _p(place_of), _stream(ids)), "moe_sort")
+    tiles = 0
+    if tile_group is not None:
+        tiles = R // pad
+        _need(tile_group, "groups of the row tiles", torch.int32, (tiles,))
+    _check(library().li_moe_sort(_p(ids), _i(n), _i(experts), _i(int(pad)), _p(offsets), _p(pair_at), _p(place_of), _p(tile_group), _i(tiles),
+                                 _i(R), _stream(ids)), "moe_sort")
 
 
 def moe_gather(h: torch.Tensor, pair_at: torch.Tensor, weights: Optional[torch.Tensor], top: int, out: torch.Tensor) -> None:
-    """``out[r] = h[pair_at[r] // top]``, times ``weights.flatten()[pair_at[r]]`` if given (the weight on the expert's input)."""
+    """``out[r] = h[pair_at[r] // top]``, times ``weights.flatten()[pair_at[r]]`` if given (the weight on the expert's input);
+    a row of zeros where ``pair_at[r]`` is negative."""
     T, H = h.shape
     n = pair_at.shape[0]
     _need(h, "feed-forward input")
-    _need(pair_at, "pair at place", torch.int32, (T * top,))
+    _need(pair_at, "pair at place", torch.int32)
     if weights is not None:
         _need(weights, "expert weights", torch.float32, (T, top))
     _need(out, "sorted rows", h.dtype, (n, H))
@@ -906,7 +927,7 @@ def moe_gather(h: torch.Tensor, pair_at: torch.Tensor, weights: Optional[torch.T
 def moe_combine(rows: torch.Tensor, place_of: torch.Tensor, weights: Optional[torch.Tensor], top: int, y: torch.Tensor) -> None:
     """``y[t] = sum_k rows[place_of[t * top + k]]`` (times ``weights[t, k]`` if given), summed in float32 in the order of k."""
     T, H = y.shape
-    _need(rows, "sorted rows", None, (T * top, H))
+    _need(rows, "sorted rows", None, (rows.shape[0], H))
     _need(place_of, "place of pair", torch.int32, (T * top,))
     if weights is not None:
         _need(weights, "expert weights", torch.float32, (T, top))

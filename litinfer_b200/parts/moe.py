@@ -7,8 +7,8 @@
     expert(u) = W_down (silu(W_gate u) * (W_up u)), no biases.
 
 How a step runs it: the router's product with a float32 result, the choice per token (one warp a token), a stable
-counting sort of the (token, choice) pairs by expert on the device, one gather that builds the experts' input rows in
-sorted order (with the weight on them), a product per expert over its run of rows for gate|up and for down
+counting sort of the (token, choice) pairs by expert on the device (in a step of many tokens every expert's run starts
+at a multiple of 128 rows), one gather that builds the experts' input rows in sorted order (with the weight on them), a product per expert over its run of rows for gate|up and for down
 (``kernels.grouped_linear`` with the row offsets the sort left on the device), and a combine that sums a token's rows in
 the order of its choices.  Nothing comes back to the host, so the launches are the same whatever the routing, and a step
 of single tokens can be captured.  A row's result does not depend on which rows share its expert.
@@ -28,6 +28,9 @@ from .linear import FusedLinear
 
 @FEED_FORWARDS.register("routed_experts")
 class RoutedExperts(FeedForward):
+    PAD = 128                      # rows of a tensor-core tile
+    PAD_FROM_ROWS = 256            # (token, choice) pairs of a step from which the runs are padded
+
     def __init__(self, spec, prefix, dtype, device):
         super().__init__(spec, prefix, dtype, device)
         self.hidden = int(spec["hidden_size"])
@@ -77,18 +80,23 @@ class RoutedExperts(FeedForward):
         ids = torch.empty((T, top), dtype=torch.int32, device=dev)
         weights = torch.empty((T, top), dtype=torch.float32, device=dev)
         K.moe_route(logits, top, ids, weights)
+        # a step of many tokens: every expert's run of rows starts at a multiple of 128, so that the products run on
+        # tensor-core tiles of 128 rows, each of one expert
+        pad = self.PAD if (self.dtype == torch.bfloat16 and T * top >= self.PAD_FROM_ROWS) else 1
+        R = K.sorted_rows(T * top, E, pad)
         offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
-        pair_at = torch.empty(T * top, dtype=torch.int32, device=dev)
+        pair_at = torch.empty(R, dtype=torch.int32, device=dev)
         place_of = torch.empty(T * top, dtype=torch.int32, device=dev)
-        K.moe_sort(ids, E, offsets, pair_at, place_of)
+        tiles = torch.empty(R // pad, dtype=torch.int32, device=dev) if pad > 1 else None
+        K.moe_sort(ids, E, offsets, pair_at, place_of, pad, tiles)
         on_input = self.weight_on == "input"
-        rows = torch.empty((T * top, self.hidden), dtype=self.dtype, device=dev)
+        rows = torch.empty((R, self.hidden), dtype=self.dtype, device=dev)
         K.moe_gather(h, pair_at, weights if on_input else None, top, rows)
-        both = torch.empty((T * top, 2 * F), dtype=self.dtype, device=dev)
-        K.grouped_linear(rows, self.gate_up, both, offsets)
-        act = torch.empty((T * top, F), dtype=self.dtype, device=dev)
+        both = torch.empty((R, 2 * F), dtype=self.dtype, device=dev)
+        K.grouped_linear(rows, self.gate_up, both, offsets, tile_group=tiles)
+        act = torch.empty((R, F), dtype=self.dtype, device=dev)
         K.swiglu(both, act)
-        K.grouped_linear(act, self.down, rows, offsets)
+        K.grouped_linear(act, self.down, rows, offsets, tile_group=tiles)
         y = torch.empty((T, self.hidden), dtype=self.dtype, device=dev)
         K.moe_combine(rows, place_of, None if on_input else weights, top, y)
         return y

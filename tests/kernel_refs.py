@@ -299,7 +299,7 @@ def conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token
     v_cache[page, :, :, off] = v
 
 
-def grouped_linear(a, weight, out, row_offsets=None, a_group_cols=0, out_group_cols=0):
+def grouped_linear(a, weight, out, row_offsets=None, a_group_cols=0, out_group_cols=0, tile_group=None):
     G, N, Kd = weight.shape
     if row_offsets is not None:
         offs = row_offsets.tolist()
@@ -321,21 +321,35 @@ def moe_route(logits, top, ids, weights):
     weights.copy_(order.values[:, :top])
 
 
-def moe_sort(ids, experts, offsets, pair_at, place_of):
+def sorted_rows(pairs, experts, pad=1):
+    return pairs if pad <= 1 else -(-(pairs + experts * (pad - 1)) // pad) * pad
+
+
+def moe_sort(ids, experts, offsets, pair_at, place_of, pad=1, tile_group=None):
     flat = ids.reshape(-1).long()
-    order = torch.sort(flat, stable=True).indices
-    pair_at.copy_(order.to(torch.int32))
-    place_of[order] = torch.arange(flat.numel(), dtype=torch.int32, device=ids.device)
-    counts = torch.bincount(flat, minlength=experts)
-    offsets[0] = 0
-    offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
+    counts = torch.bincount(flat, minlength=experts).tolist()
+    pair_at.fill_(-1)
+    if tile_group is not None:
+        tile_group.fill_(-1)
+    start = 0
+    for e in range(experts):
+        mine = torch.nonzero(flat == e).reshape(-1)                  # ascending: the order of the pairs
+        offsets[e] = start
+        pair_at[start:start + counts[e]] = mine.to(torch.int32)
+        place_of[mine] = torch.arange(start, start + counts[e], dtype=torch.int32, device=ids.device)
+        run = -(-counts[e] // pad) * pad
+        if tile_group is not None:
+            tile_group[start // pad:(start + run) // pad] = e
+        start += run
+    offsets[experts] = start
 
 
 def moe_gather(h, pair_at, weights, top, out):
-    src = h[(pair_at // top).long()].float()
+    at = pair_at.long().clamp_min(0)
+    src = h[at // top].float()
     if weights is not None:
-        src = src * weights.reshape(-1)[pair_at.long()][:, None]
-    _store(out, src)
+        src = src * weights.reshape(-1)[at][:, None]
+    _store(out, src * (pair_at >= 0).float()[:, None])
 
 
 def moe_combine(rows, place_of, weights, top, y):
@@ -565,7 +579,7 @@ def table_gather(resident, updates, slots, out, trash_page):
             out[s, b] = resident[slot, b] if b < cols else trash_page
 
 
-ALL = ["norm_add_norm", "add_row", "rmsnorm_cols", "conv_norm_rope_kv", "grouped_linear", "moe_route", "moe_sort", "moe_gather", "moe_combine",
+ALL = ["sorted_rows", "norm_add_norm", "add_row", "rmsnorm_cols", "conv_norm_rope_kv", "grouped_linear", "moe_route", "moe_sort", "moe_gather", "moe_combine",
        "glu_clamped", "weighted_sum2", "add_position_rows", "hc_expand", "hc_read_norm", "hc_update", "causal_conv_silu", "conv_state_shift", "ssm_scan",
        "decay_scan", "gated_rmsnorm", "table_gather", "gather_rows", "scale_inplace", "logit_cap", "rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]

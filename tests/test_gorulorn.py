@@ -668,6 +668,36 @@ def test_products_in_groups_and_routing_kernels(dtype):
         _close(rows[0], rows[1], dtype, "gathered rows")
         _close(outs[0], outs[1], dtype, "rows in groups")
         _close(ys[0], ys[1], dtype, "combined")
+    # many rows: every expert's run starts at a multiple of 128 and the products take tensor-core tiles of one expert each
+    for T, E, top, H, F in ((700, 5, 2, 64, 136), (2048, 8, 1, 256, 96), (300, 16, 3, 72, 40)):
+        logits = (2.0 * torch.randn(T, E)).to(dev)
+        if E == 16:
+            logits[:, 3] = -30.0                              # an expert nobody chooses: an empty run
+        ids = torch.empty(T, top, dtype=torch.int32, device=dev)
+        wts = torch.empty(T, top, dtype=torch.float32, device=dev)
+        K.moe_route(logits, top, ids, wts)
+        n_rows = K.sorted_rows(T * top, E, 128)
+        assert n_rows % 128 == 0 and n_rows >= T * top
+        srt = [[torch.empty(E + 1, dtype=torch.int32, device=dev), torch.empty(n_rows, dtype=torch.int32, device=dev),
+                torch.empty(T * top, dtype=torch.int32, device=dev), torch.empty(n_rows // 128, dtype=torch.int32, device=dev)] for _ in range(2)]
+        K.moe_sort(ids, E, srt[0][0], srt[0][1], srt[0][2], 128, srt[0][3])
+        R.moe_sort(ids, E, srt[1][0], srt[1][1], srt[1][2], 128, srt[1][3])
+        upto = int(srt[1][0][-1])
+        assert torch.equal(srt[0][0], srt[1][0]) and torch.equal(srt[0][2], srt[1][2]) and torch.equal(srt[0][3], srt[1][3])
+        assert torch.equal(srt[0][1], srt[1][1])
+        offsets, pair_at, place_of, tiles = srt[0]
+        h = torch.randn(T, H).to(dev, dt)
+        w1 = (torch.randn(E, F, H) / math.sqrt(H)).to(dev, dt)
+        rows = [torch.empty(n_rows, H, dtype=dt, device=dev) for _ in range(2)]
+        outs = [torch.zeros(n_rows, F, dtype=dt, device=dev) for _ in range(2)]
+        ys = [torch.empty(T, F, dtype=dt, device=dev) for _ in range(2)]
+        for i, Fn in enumerate((K, R)):
+            Fn.moe_gather(h, pair_at, wts, top, rows[i])
+            Fn.grouped_linear(rows[i], w1, outs[i], offsets, tile_group=tiles)
+            Fn.moe_combine(outs[i], place_of, None, top, ys[i])
+        _close(rows[0], rows[1], dtype, "gathered rows (padded runs)")
+        _close(outs[0][:upto], outs[1][:upto], dtype, "rows in groups (padded runs)")
+        _close(ys[0], ys[1], dtype, "combined (padded runs)")
     # a map per head: columns in groups
     G, M, Kd, N = 5, 77, 24, 40
     a = torch.randn(M, G * Kd + 3).to(dev, dt)
