@@ -125,7 +125,9 @@ __device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1
 // TM 64: many rows a group (portions of prompts); a warp takes 16 rows and all 64 columns.  TM 16: few rows a group
 // (single tokens: the weights are what is read): a warp takes all 16 rows and 16 of the columns, and four stages of
 // 64 elements keep more of the weights on their way.
-template <int TM, int TK, int ST>
+// kSwiglu: the columns come as 8 gate, 8 up, 8 gate, 8 up, ... (the rows of every group's matrix interleaved in eights), and
+// out [M, N / 2] takes up * gate / (1 + exp(-gate)): a thread holds a gate column and its up column in neighbouring tiles of 8.
+template <int TM, int TK, int ST, bool kSwiglu>
 __global__ void __launch_bounds__(128)
 grouped_mma_kernel(const bf16* __restrict__ A, int lda, int a_gcol, const bf16* __restrict__ W, bf16* __restrict__ C, int ldc, int c_gcol,
                    const int* __restrict__ row_offsets, int M, int N, int K, int G) {
@@ -203,6 +205,21 @@ grouped_mma_kernel(const bf16* __restrict__ A, int lda, int a_gcol, const bf16* 
         }
     }
     const int r_lo = m0 + row0 + gq, r_hi = r_lo + 8;
+    if constexpr (kSwiglu) {
+#pragma unroll
+        for (int j = 0; j < NT; j += 2) {
+            const int gate_col = n0 + col0 + j * 8 + 2 * t;           // its up column stands 8 further on
+            const int n = (n0 + col0 + j * 8) / 2 + 2 * t;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if (gate_col + i + 8 < N) {
+                    if (r_lo < m_end) c[(size_t)r_lo * ldc + n + i] = __float2bfloat16_rn(swiglu_of<bf16>(acc[j][i], acc[j + 1][i]));
+                    if (r_hi < m_end) c[(size_t)r_hi * ldc + n + i] = __float2bfloat16_rn(swiglu_of<bf16>(acc[j][2 + i], acc[j + 1][2 + i]));
+                }
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
         const int n = n0 + col0 + j * 8 + 2 * t;
@@ -357,38 +374,49 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __rest
 
 }  // namespace
 
-int li_linear_tcgen05_grouped(const void* a, const void* w, void* out, int M, int N, int K, int G, const int* tile_group, cudaStream_t stream);
+int li_linear_tcgen05_grouped(const void* a, const void* w, void* out, int M, int N, int K, int G, const int* tile_group, int swiglu,
+                              cudaStream_t stream);
 
 // tile_group (may be NULL; rows in groups whose runs start at multiples of 128, li_moe_sort with pad 128): the group of
 // every tile of 128 rows; bfloat16 products of at least kTensorRows rows then run on tcgen05 tiles.
 constexpr int kTensorRows = 256;
 
+// epilogue: LI_EPILOGUE_NONE, or LI_EPILOGUE_SWIGLU (bfloat16, K a multiple of 8, N a multiple of 16): gate and up rows of
+// every group's matrix interleaved in eights, out rows of N / 2 activations.
 LI_EXPORT int li_grouped_linear(const void* a, int lda, int a_gcol, const void* w, void* out, int ldc, int c_gcol, const int* row_offsets,
-                                const int* tile_group, int dtype, int M, int N, int K, int G, cudaStream_t stream) {
+                                const int* tile_group, int dtype, int M, int N, int K, int G, int epilogue, cudaStream_t stream) {
     LI_REQUIRE(M >= 0 && N > 0 && K > 0 && G > 0, "grouped_linear: bad sizes M=%d N=%d K=%d G=%d", M, N, K, G);
-    LI_REQUIRE(lda >= K && ldc >= N, "grouped_linear: rows of %d and %d elements cannot hold K=%d and N=%d", lda, ldc, K, N);
+    LI_REQUIRE(epilogue == LI_EPILOGUE_NONE || epilogue == LI_EPILOGUE_SWIGLU, "grouped_linear: unknown epilogue %d", epilogue);
+    const bool swiglu = epilogue == LI_EPILOGUE_SWIGLU;
+    const int out_cols = swiglu ? N / 2 : N;
+    LI_REQUIRE(lda >= K && ldc >= out_cols, "grouped_linear: rows of %d and %d elements cannot hold K=%d and %d outputs", lda, ldc, K, out_cols);
     LI_REQUIRE(row_offsets == nullptr || (a_gcol == 0 && c_gcol == 0), "grouped_linear: groups are rows or columns, not both");
     LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "grouped_linear: unknown dtype %d", dtype);
     if (M == 0) return 0;
-    if (dtype == LI_BF16 && row_offsets != nullptr && tile_group != nullptr && M >= kTensorRows && M % 128 == 0 && lda == K && ldc == N &&
-        K % 8 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0)
-        return li_linear_tcgen05_grouped(a, w, out, M, N, K, G, tile_group, stream);
+    if (dtype == LI_BF16 && row_offsets != nullptr && tile_group != nullptr && M >= kTensorRows && M % 128 == 0 && lda == K && ldc == out_cols &&
+        K % 8 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0 && (!swiglu || N % 16 == 0))
+        return li_linear_tcgen05_grouped(a, w, out, M, N, K, G, tile_group, swiglu ? 1 : 0, stream);
     const int row_tiles = ceil_div(M, BM);
     const dim3 grid(ceil_div(N, BN), row_offsets ? row_tiles + G : row_tiles, row_offsets ? 1 : G);
     LI_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "grouped_linear: too many tiles for one launch");
     cudaError_t e;
     // 16-byte copies: every row and every group's first column on a 16-byte boundary
     const bool aligned = K % 8 == 0 && lda % 8 == 0 && a_gcol % 8 == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0;
+    LI_REQUIRE(!swiglu || (dtype == LI_BF16 && aligned && N % 16 == 0), "grouped_linear: the swiglu epilogue takes bfloat16, K a multiple of 8 and N a multiple of 16");
     // few rows a group (single tokens): tiles of 16 rows, more of the weights in flight
     const bool few = row_offsets ? M <= 32 * G : M <= 32;
     if (dtype == LI_BF16 && aligned && few) {
         const int tiles16 = ceil_div(M, 16);
         const dim3 grid16(ceil_div(N, BN), row_offsets ? tiles16 + G : tiles16, row_offsets ? 1 : G);
-        e = li_launch_pdl(grouped_mma_kernel<16, 64, 4>, grid16, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w, (bf16*)out, ldc,
-                          c_gcol, row_offsets, M, N, K, G);
+        e = swiglu ? li_launch_pdl(grouped_mma_kernel<16, 64, 4, true>, grid16, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w,
+                                   (bf16*)out, ldc, c_gcol, row_offsets, M, N, K, G)
+                   : li_launch_pdl(grouped_mma_kernel<16, 64, 4, false>, grid16, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w,
+                                   (bf16*)out, ldc, c_gcol, row_offsets, M, N, K, G);
     } else if (dtype == LI_BF16 && aligned)
-        e = li_launch_pdl(grouped_mma_kernel<64, 32, 3>, grid, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w, (bf16*)out, ldc, c_gcol,
-                          row_offsets, M, N, K, G);
+        e = swiglu ? li_launch_pdl(grouped_mma_kernel<64, 32, 3, true>, grid, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w,
+                                   (bf16*)out, ldc, c_gcol, row_offsets, M, N, K, G)
+                   : li_launch_pdl(grouped_mma_kernel<64, 32, 3, false>, grid, dim3(128), 0, stream, (const bf16*)a, lda, a_gcol, (const bf16*)w,
+                                   (bf16*)out, ldc, c_gcol, row_offsets, M, N, K, G);
     else if (dtype == LI_F32)
         e = li_launch_pdl(grouped_linear_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)a, lda, a_gcol, (const float*)w, (float*)out,
                           ldc, c_gcol, row_offsets, M, N, K, G);

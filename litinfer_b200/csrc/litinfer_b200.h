@@ -245,9 +245,10 @@ int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* co
 /* out_g = a_g w_g^T, w [G, N, K].  row_offsets [G + 1] (device): group g owns those rows of a [M, lda] and out [M, ldc].
  * row_offsets NULL: every group takes all M rows, inputs at column g * a_gcol, outputs at column g * c_gcol.
  * tile_group (may be NULL): with runs of rows that start at multiples of 128, the group of every tile of 128 rows (-1: none);
- * large bfloat16 products then run on tcgen05 tiles. */
+ * large bfloat16 products then run on tcgen05 tiles.  epilogue 1 (bfloat16): gate and up rows of every matrix interleaved in
+ * eights, out rows of N / 2 activations up * gate / (1 + exp(-gate)). */
 int li_grouped_linear(const void* a, int lda, int a_gcol, const void* w, void* out, int ldc, int c_gcol, const int* row_offsets,
-    const int* tile_group, int dtype, int M, int N, int K, int G, cudaStream_t stream);
+    const int* tile_group, int dtype, int M, int N, int K, int G, int epilogue, cudaStream_t stream);
 
 /* ids, weights [T, top]: the experts with the largest sigmoid(logits [T, E]) and those scores. */
 int li_moe_route(const float* logits, int T, int E, int top, int* ids, float* weights, cudaStream_t stream);

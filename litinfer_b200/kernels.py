@@ -849,13 +849,24 @@ def conv_norm_rope_kv(proj: torch.Tensor, out: torch.Tensor, conv_w: Optional[to
 # --------------------------------------------------------------------------
 
 def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_offsets: Optional[torch.Tensor] = None,
-                   a_group_cols: int = 0, out_group_cols: int = 0, tile_group: Optional[torch.Tensor] = None) -> None:
+                   a_group_cols: int = 0, out_group_cols: int = 0, tile_group: Optional[torch.Tensor] = None,
+                   epilogue: Optional[str] = None) -> None:
     """``weight`` [G, N, K]: a product per group.  With ``row_offsets`` (int32 [G + 1] on the device) group g owns the rows
     ``row_offsets[g] .. row_offsets[g + 1] - 1`` of ``a`` [M, K] and ``out`` [M, N].  Without, every group takes all rows, its
     inputs at column ``g * a_group_cols`` of ``a`` and its outputs at column ``g * out_group_cols`` of ``out`` (a map per head).
     ``tile_group`` (int32 on the device; from :func:`moe_sort` with ``pad`` 128): the group of every tile of 128 rows when
-    the groups' runs start at multiples of 128; large bfloat16 products then run on the tcgen05 tiles."""
+    the groups' runs start at multiples of 128; large bfloat16 products then run on the tcgen05 tiles.
+    ``epilogue="swiglu"`` (bfloat16, rows in groups): every group's matrix holds gate and up rows interleaved in eights
+    (:func:`interleave_gate_up` per group) and ``out`` [M, N / 2] takes ``up * gate / (1 + exp(-gate))``."""
     G, N, Kd = weight.shape
+    if epilogue not in (None, "swiglu"):
+        raise KernelError(f"grouped_linear: unknown epilogue {epilogue!r}")
+    if epilogue == "swiglu":
+        if a.dtype != torch.bfloat16 or row_offsets is None or N % 16 or Kd % 8:
+            raise KernelError("grouped_linear: the swiglu epilogue takes bfloat16 rows in groups, K a multiple of 8, N a multiple of 16")
+        N_out = N // 2
+    else:
+        N_out = N
     M = a.shape[0]
     _need(a, "grouped input")
     _need(weight, "grouped weights", a.dtype)
@@ -864,8 +875,8 @@ def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row
         raise KernelError(f"grouped_linear: {out.shape[0]} output rows for {M} input rows")
     if row_offsets is not None:
         _need(row_offsets, "row offsets", torch.int32, (G + 1,))
-        if a.shape[1] != Kd or out.shape[1] != N or a_group_cols or out_group_cols:
-            raise KernelError(f"grouped_linear: rows in groups need a [M, {Kd}] and out [M, {N}]")
+        if a.shape[1] != Kd or out.shape[1] != N_out or a_group_cols or out_group_cols:
+            raise KernelError(f"grouped_linear: rows in groups need a [M, {Kd}] and out [M, {N_out}]")
     elif (G - 1) * a_group_cols + Kd > a.shape[1] or (G - 1) * out_group_cols + N > out.shape[1]:
         raise KernelError("grouped_linear: the groups' columns do not fit the rows")
     if tile_group is not None:
@@ -873,7 +884,8 @@ def grouped_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row
         if row_offsets is None or tile_group.numel() * 128 < M:
             raise KernelError("grouped_linear: a table of the tiles' groups goes with row offsets and covers every tile of 128 rows")
     _check(library().li_grouped_linear(_p(a), _i(a.shape[1]), _i(a_group_cols), _p(weight), _p(out), _i(out.shape[1]), _i(out_group_cols),
-                                       _p(row_offsets), _p(tile_group), _i(_dt(a)), _i(M), _i(N), _i(Kd), _i(G), _stream(out)), "grouped_linear")
+                                       _p(row_offsets), _p(tile_group), _i(_dt(a)), _i(M), _i(N), _i(Kd), _i(G), _i(EPILOGUES[epilogue]), _stream(out)),
+           "grouped_linear")
 
 
 def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:

@@ -55,6 +55,9 @@ class RoutedExperts(FeedForward):
         self.expert_names = [tuple(prefix + stem.format(e) + n.get(k, d) + w for k, d in (("gate", "gate_proj"), ("up", "up_proj"), ("down", "down_proj")))
                              for e in range(self.experts)]
         self.gate_up = self.down = None                       # [E, 2 F, hidden] (gate rows, then up rows) and [E, hidden, F]
+        # bfloat16 with sizes that are multiples of 8: gate and up rows of every expert interleaved in eights when bound, and
+        # the gated activation is the epilogue of the grouped product (the [rows, 2 F] product never goes to memory)
+        self.fused_activation = dtype == torch.bfloat16 and self.intermediate % 8 == 0 and self.hidden % 8 == 0
 
     def params(self) -> List[ParamSpec]:
         out = self.router.params()
@@ -67,7 +70,8 @@ class RoutedExperts(FeedForward):
         self.router.bind(tensors)
         gu, dn = [], []
         for g, u, d in self.expert_names:
-            gu.append(torch.cat([tensors.pop(g), tensors.pop(u)], dim=0))
+            gate, up = tensors.pop(g), tensors.pop(u)
+            gu.append(K.interleave_gate_up(gate, up) if self.fused_activation else torch.cat([gate, up], dim=0))
             dn.append(tensors.pop(d))
         self.gate_up = torch.stack(gu).contiguous()
         self.down = torch.stack(dn).contiguous()
@@ -92,10 +96,13 @@ class RoutedExperts(FeedForward):
         on_input = self.weight_on == "input"
         rows = torch.empty((R, self.hidden), dtype=self.dtype, device=dev)
         K.moe_gather(h, pair_at, weights if on_input else None, top, rows)
-        both = torch.empty((R, 2 * F), dtype=self.dtype, device=dev)
-        K.grouped_linear(rows, self.gate_up, both, offsets, tile_group=tiles)
         act = torch.empty((R, F), dtype=self.dtype, device=dev)
-        K.swiglu(both, act)
+        if self.fused_activation:
+            K.grouped_linear(rows, self.gate_up, act, offsets, tile_group=tiles, epilogue="swiglu")
+        else:
+            both = torch.empty((R, 2 * F), dtype=self.dtype, device=dev)
+            K.grouped_linear(rows, self.gate_up, both, offsets, tile_group=tiles)
+            K.swiglu(both, act)
         K.grouped_linear(act, self.down, rows, offsets, tile_group=tiles)
         y = torch.empty((T, self.hidden), dtype=self.dtype, device=dev)
         K.moe_combine(rows, place_of, None if on_input else weights, top, y)

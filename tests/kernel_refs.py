@@ -299,14 +299,19 @@ def conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token
     v_cache[page, :, :, off] = v
 
 
-def grouped_linear(a, weight, out, row_offsets=None, a_group_cols=0, out_group_cols=0, tile_group=None):
+def grouped_linear(a, weight, out, row_offsets=None, a_group_cols=0, out_group_cols=0, tile_group=None, epilogue=None):
     G, N, Kd = weight.shape
     if row_offsets is not None:
         offs = row_offsets.tolist()
         for g in range(G):
             lo, hi = offs[g], offs[g + 1]
             if hi > lo:
-                out[lo:hi] = (a[lo:hi].float() @ weight[g].float().t()).to(out.dtype)
+                y = a[lo:hi].float() @ weight[g].float().t()
+                if epilogue == "swiglu":
+                    y = y.view(hi - lo, N // 16, 2, 8)                 # columns come as 8 gate, 8 up, 8 gate, 8 up, ...
+                    gate, up = y[:, :, 0, :], y[:, :, 1, :]
+                    y = (up * (gate / (1.0 + torch.exp(-gate)))).reshape(hi - lo, N // 2)
+                out[lo:hi] = y.to(out.dtype)
         return
     for g in range(G):
         out[:, g * out_group_cols:g * out_group_cols + N] = (a[:, g * a_group_cols:g * a_group_cols + Kd].float() @ weight[g].float().t()).to(out.dtype)

@@ -642,7 +642,7 @@ def test_products_in_groups_and_routing_kernels(dtype):
 
     dev, dt = torch.device("cuda:0"), _dt(dtype)
     torch.manual_seed(3)
-    for T, E, top, H, F in ((1, 4, 2, 40, 24), (150, 7, 3, 72, 100), (64, 1, 1, 32, 16), (333, 40, 4, 48, 8)):
+    for T, E, top, H, F in ((1, 4, 2, 40, 32), (150, 7, 3, 72, 96), (64, 1, 1, 32, 16), (333, 40, 4, 48, 8), (9, 8, 2, 64, 100)):
         logits = (2.0 * torch.randn(T, E)).to(dev)
         ids = [torch.empty(T, top, dtype=torch.int32, device=dev) for _ in range(2)]
         wts = [torch.empty(T, top, dtype=torch.float32, device=dev) for _ in range(2)]
@@ -668,8 +668,13 @@ def test_products_in_groups_and_routing_kernels(dtype):
         _close(rows[0], rows[1], dtype, "gathered rows")
         _close(outs[0], outs[1], dtype, "rows in groups")
         _close(ys[0], ys[1], dtype, "combined")
+        if dtype == "bfloat16" and F % 16 == 0:                 # the gated activation as the product's epilogue
+            acts = [torch.empty(T * top, F // 2, dtype=dt, device=dev) for _ in range(2)]
+            K.grouped_linear(rows[0], w1, acts[0], offsets, epilogue="swiglu")
+            R.grouped_linear(rows[0], w1, acts[1], offsets, epilogue="swiglu")
+            _close(acts[0], acts[1], dtype, "gated rows in groups")
     # many rows: every expert's run starts at a multiple of 128 and the products take tensor-core tiles of one expert each
-    for T, E, top, H, F in ((700, 5, 2, 64, 136), (2048, 8, 1, 256, 96), (300, 16, 3, 72, 40)):
+    for T, E, top, H, F in ((700, 5, 2, 64, 144), (2048, 8, 1, 256, 1056), (300, 16, 3, 72, 40)):
         logits = (2.0 * torch.randn(T, E)).to(dev)
         if E == 16:
             logits[:, 3] = -30.0                              # an expert nobody chooses: an empty run
@@ -695,6 +700,11 @@ def test_products_in_groups_and_routing_kernels(dtype):
             Fn.moe_gather(h, pair_at, wts, top, rows[i])
             Fn.grouped_linear(rows[i], w1, outs[i], offsets, tile_group=tiles)
             Fn.moe_combine(outs[i], place_of, None, top, ys[i])
+        if dtype == "bfloat16" and F % 16 == 0:
+            acts = [torch.zeros(n_rows, F // 2, dtype=dt, device=dev) for _ in range(2)]
+            K.grouped_linear(rows[0], w1, acts[0], offsets, tile_group=tiles, epilogue="swiglu")
+            R.grouped_linear(rows[0], w1, acts[1], offsets, tile_group=tiles, epilogue="swiglu")
+            _close(acts[0][:upto], acts[1][:upto], dtype, "gated rows in groups (padded runs)")
         _close(rows[0], rows[1], dtype, "gathered rows (padded runs)")
         _close(outs[0][:upto], outs[1][:upto], dtype, "rows in groups (padded runs)")
         _close(ys[0], ys[1], dtype, "combined (padded runs)")
