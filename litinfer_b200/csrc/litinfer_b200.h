@@ -219,9 +219,11 @@ int li_linear_rope_kv(const void* a, const void* w, const float* bias, void* qkv
 /* ---- norm_pair.cu: norms before and after a sublayer in one pass over the residual stream ---- */
 /* Per row: x += post(y) (post: a norm of y [R, H] with the weight w_post; NULL: x += y; y NULL: nothing is added), then
  * out = next(x) if w_next is given.  A norm is centered (mean taken off, variance as the mean of squared deviations:
- * layer norm without bias) or not (RMS norm).  rows (may be NULL; only without y): out[r] = next(x[rows[r]]). */
+ * layer norm without bias) or not (RMS norm).  rows (may be NULL; only without y): out[r] = next(x[rows[r]]).
+ * y_places (may be NULL): token r's y is the sum over j < y_top of y[y_places[r y_top + j]] (times y_weights[...] if given). */
 int li_norm_add_norm(float* x, const void* y, int dtype, const float* w_post, int post_centered, float eps_post, const float* w_next,
-    int next_centered, float eps_next, void* out, const int* rows, int R, int n_src, int H, cudaStream_t stream);
+    int next_centered, float eps_next, void* out, const int* rows, int R, int n_src, int H, const int* y_places,
+    int y_top, const float* y_weights, cudaStream_t stream);
 
 /* x[t] += row for every token. */
 int li_add_row(float* x, const float* row, int T, int H, cudaStream_t stream);
@@ -234,12 +236,14 @@ int li_rmsnorm_cols(const void* in, int dtype, int ld_in, int col, int n, int wi
 /* ---- qkv_post.cu: between the q|k|v product and attention ---- */
 /* A short causal convolution per channel (conv_w [(nh + 2 nkv) dh, taps]; inputs before a portion from state [slots,
  * state_stride] at state_off), an RMS norm per query and key head (q_norm, k_norm [dh], mean over norm_width elements),
- * the rotation of the first rotary_dim elements, q to out, k and v into the paged cache.  Every step is optional. */
-int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* conv_w, int taps, const float* state,
+ * the rotation of the first rotary_dim elements, q to out, k and v into the paged cache.  Every step is optional.
+ * shift: every sequence of the step has one token, and the state moves on in the same launch.  to_cache 0: keys and values
+ * go to their columns of out, not into the cache. */
+int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* conv_w, int taps, float* state,
     long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
     const float* q_norm, const float* k_norm, float eps, int norm_width, const int* positions, const float* denom,
     int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T, int nh, int nkv, int dh,
-    int page_size, int num_pages, int write, cudaStream_t stream);
+    int page_size, int num_pages, int write, int shift, int to_cache, cudaStream_t stream);
 
 /* ---- grouped.cu: products in groups, routing of a mixture of experts ---- */
 /* out_g = a_g w_g^T, w [G, N, K].  row_offsets [G + 1] (device): group g owns those rows of a [M, lda] and out [M, ldc].

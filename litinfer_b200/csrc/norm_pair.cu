@@ -10,9 +10,9 @@
 //   li_add_row: x[t] += table[row] for every token (a vector per pass of a looped span of layers).
 //   li_rmsnorm_cols: RMS norm of n columns of a run-dtype matrix, written to (up to) two places of another matrix.
 //
-// All sums, means and the residual stream are float; y and out are in the run dtype.  One block per row; the row is
-// read again from cache for the second moment, so that the variance is the mean of squared deviations, not a
-// difference of large sums.
+// All sums, means and the residual stream are float; y and out are in the run dtype.  One block per row.  The variance
+// is the mean of squared deviations, not a difference of large sums: rows of up to 8,192 elements are held in registers
+// for that (read once), longer ones are read again from cache.
 #include "common.cuh"
 
 namespace {
@@ -68,6 +68,112 @@ __global__ void norm_add_norm_kernel(float* __restrict__ x, const T* __restrict_
     }
 }
 
+// The same with the row in registers: thread i holds elements i, i + blockDim, ... (up to kRegs of them), so the row of y
+// and the row of x are read once and every moment is taken from registers.  H <= kRegs * blockDim.
+constexpr int kRegs = 8;
+
+template <typename T>
+__global__ void norm_add_norm_regs_kernel(float* __restrict__ x, const T* __restrict__ y, const float* __restrict__ w_post, int post_centered,
+                                          float eps_post, const float* __restrict__ w_next, int next_centered, float eps_next,
+                                          T* __restrict__ out, const int* __restrict__ rows, int n_src, int H,
+                                          const int* __restrict__ y_places, int y_top, const float* __restrict__ y_weights) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    int src = r;
+    if (rows) {
+        src = rows[r];
+        if (src < 0 || src >= n_src) src = 0;
+    }
+    float* xr = x + (size_t)src * H;
+    const float inv_h = 1.0f / (float)H;
+    float xv[kRegs];
+#pragma unroll
+    for (int k = 0; k < kRegs; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        xv[k] = i < H ? xr[i] : 0.0f;
+    }
+    if (y) {
+        float yv[kRegs];
+        if (y_places) {
+            // the sublayer's output for this token is a sum of rows that lie elsewhere (a token's experts), taken in float
+            // in the order of the list
+#pragma unroll
+            for (int k = 0; k < kRegs; ++k) yv[k] = 0.0f;
+            for (int j = 0; j < y_top; ++j) {
+                const T* yr = y + (size_t)y_places[(size_t)r * y_top + j] * H;
+                const float f = y_weights ? y_weights[(size_t)r * y_top + j] : 1.0f;
+#pragma unroll
+                for (int k = 0; k < kRegs; ++k) {
+                    const int i = threadIdx.x + k * blockDim.x;
+                    if (i < H) yv[k] = fmaf(f, to_float(yr[i]), yv[k]);
+                }
+            }
+        } else {
+            const T* yr = y + (size_t)r * H;
+#pragma unroll
+            for (int k = 0; k < kRegs; ++k) {
+                const int i = threadIdx.x + k * blockDim.x;
+                yv[k] = i < H ? to_float(yr[i]) : 0.0f;
+            }
+        }
+        if (w_post) {
+            float mean = 0.0f;
+            if (post_centered) {
+                float s = 0.0f;
+#pragma unroll
+                for (int k = 0; k < kRegs; ++k) s += yv[k];
+                mean = block_sum(s, scratch) * inv_h;
+            }
+            float q = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kRegs; ++k) {
+                const int i = threadIdx.x + k * blockDim.x;
+                const float d = i < H ? yv[k] - mean : 0.0f;
+                q = fmaf(d, d, q);
+            }
+            const float rinv = 1.0f / sqrtf(block_sum(q, scratch) * inv_h + eps_post);
+#pragma unroll
+            for (int k = 0; k < kRegs; ++k) {
+                const int i = threadIdx.x + k * blockDim.x;
+                if (i < H) xv[k] += (yv[k] - mean) * rinv * w_post[i];
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < kRegs; ++k) xv[k] += yv[k];
+        }
+#pragma unroll
+        for (int k = 0; k < kRegs; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < H) xr[i] = xv[k];
+        }
+    }
+    if (w_next) {
+        float mean = 0.0f;
+        if (next_centered) {
+            float s = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kRegs; ++k) s += xv[k];
+            mean = block_sum(s, scratch) * inv_h;
+        }
+        float q = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kRegs; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            const float d = i < H ? xv[k] - mean : 0.0f;
+            q = fmaf(d, d, q);
+        }
+        const float rinv = 1.0f / sqrtf(block_sum(q, scratch) * inv_h + eps_next);
+        T* o = out + (size_t)r * H;
+#pragma unroll
+        for (int k = 0; k < kRegs; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < H) o[i] = from_float<T>((xv[k] - mean) * rinv * w_next[i]);
+        }
+    }
+}
+
 __global__ void add_row_kernel(float* __restrict__ x, const float* __restrict__ row, long long n, int H) {
     pdl_launch_dependents();
     pdl_wait();
@@ -101,15 +207,32 @@ __global__ void rmsnorm_cols_kernel(const T* __restrict__ in, int ld_in, int col
 
 // y (may be NULL): [R, H] in the run dtype; w_post (may be NULL: x += y); w_next (may be NULL: no output); rows (may
 // be NULL; only without y): out[r] = next(x[rows[r]]).  x is [n_src, H] float and is changed in place when y is given.
+// y_places (may be NULL; H up to 8,192): token r's y is the sum over j < y_top of y[y_places[r y_top + j]] (times
+// y_weights[r y_top + j] if given), summed in float in that order: the combine of a mixture of experts, not written out.
 LI_EXPORT int li_norm_add_norm(float* x, const void* y, int dtype, const float* w_post, int post_centered, float eps_post, const float* w_next,
-                               int next_centered, float eps_next, void* out, const int* rows, int R, int n_src, int H, cudaStream_t stream) {
+                               int next_centered, float eps_next, void* out, const int* rows, int R, int n_src, int H, const int* y_places,
+                               int y_top, const float* y_weights, cudaStream_t stream) {
+    LI_REQUIRE(y_places == nullptr || (y != nullptr && y_top > 0 && H <= 8 * 1024), "norm_add_norm: a sum of rows needs the rows, a count and at most 8192 columns");
     LI_REQUIRE(R >= 0 && H > 0 && n_src >= 0, "norm_add_norm: bad sizes R=%d H=%d", R, H);
     LI_REQUIRE(y == nullptr || rows == nullptr, "norm_add_norm: gathered rows cannot take a sublayer's output");
     LI_REQUIRE(w_next == nullptr || out != nullptr, "norm_add_norm: a following norm needs an output");
     LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "norm_add_norm: unknown dtype %d", dtype);
     if (R == 0) return 0;
-    const int threads = H >= 2048 ? 512 : H >= 512 ? 256 : 128;
     cudaError_t e;
+    if (H <= kRegs * 1024) {
+        // the row in registers: as few threads as hold it, a multiple of 32, at least 64
+        int threads = ((ceil_div(H, kRegs) + 31) / 32) * 32;
+        if (threads < 64) threads = 64;
+        if (dtype == LI_F32)
+            e = li_launch_pdl(norm_add_norm_regs_kernel<float>, dim3(R), dim3(threads), 0, stream, x, (const float*)y, w_post, post_centered, eps_post,
+                              w_next, next_centered, eps_next, (float*)out, rows, n_src, H, y_places, y_top, y_weights);
+        else
+            e = li_launch_pdl(norm_add_norm_regs_kernel<bf16>, dim3(R), dim3(threads), 0, stream, x, (const bf16*)y, w_post, post_centered, eps_post,
+                              w_next, next_centered, eps_next, (bf16*)out, rows, n_src, H, y_places, y_top, y_weights);
+        if (e != cudaSuccess) return li_fail("norm_add_norm: launch failed: %s", cudaGetErrorString(e));
+        return li_check_launch("norm_add_norm");
+    }
+    const int threads = 512;
     if (dtype == LI_F32)
         e = li_launch_pdl(norm_add_norm_kernel<float>, dim3(R), dim3(threads), 0, stream, x, (const float*)y, w_post, post_centered, eps_post,
                           w_next, next_centered, eps_next, (float*)out, rows, n_src, H);

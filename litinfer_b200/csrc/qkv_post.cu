@@ -19,17 +19,19 @@ namespace {
 constexpr int kWarps = 4;
 constexpr int kPerLane = 16;        // head_dim <= 512
 
-template <typename T>
+// TAPS: the taps at compile time (their loads are then all in flight at once), or 0: any number, at run time.
+template <typename T, int TAPS>
 __global__ void __launch_bounds__(kWarps * 32)
-conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const float* __restrict__ conv_w, int taps,
-                         const float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ q_start,
+conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const float* __restrict__ conv_w, int taps_rt,
+                         float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ q_start,
                          const int* __restrict__ seq_of_token, const int* __restrict__ slots, const float* __restrict__ q_norm,
                          const float* __restrict__ k_norm, float eps, int norm_width, const int* __restrict__ positions,
                          const float* __restrict__ denom, int rotary_dim, const int* __restrict__ slot_mapping, T* __restrict__ kcache,
-                         T* __restrict__ vcache, int total, int nh, int nkv, int dh, int page_size, int num_pages, int write) {
+                         T* __restrict__ vcache, int total, int nh, int nkv, int dh, int page_size, int num_pages, int write, int shift, int to_cache) {
     extern __shared__ float smem[];
     pdl_launch_dependents();
     pdl_wait();
+    const int taps = TAPS > 0 ? TAPS : taps_rt;
     const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int unit = blockIdx.x * kWarps + warp_in_block;
     if (unit >= total) return;
@@ -46,17 +48,24 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
         const int s = seq_of_token[t];
         const int q0 = q_start[s];
         const int li = t - q0;
-        const float* st = taps > 1 ? state + (size_t)slots[s] * state_stride + state_off : nullptr;      // one tap reads no older row
+        float* st = taps > 1 ? state + (size_t)slots[s] * state_stride + state_off : nullptr;      // one tap reads no older row
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) {
             const int d = lane + 32 * i;
             float acc = 0.0f;
             if (i < per && d < dh) {
                 const int c = c0 + d;
-                for (int j = 0; j < taps; ++j) {
+#pragma unroll
+                for (int j = 0; j < (TAPS > 0 ? TAPS : taps); ++j) {
                     const int src = li - (taps - 1) + j;
                     const float u = src >= 0 ? to_float(proj[(size_t)(q0 + src) * N + c]) : st[(size_t)(taps - 1 + src) * N + c];
                     acc = fmaf(conv_w[(size_t)c * taps + j], u, acc);
+                }
+                if (shift && taps > 1) {
+                    // a step of single tokens: nobody else reads this channel of this sequence's state, so it moves on here
+                    // (oldest first; the newest row is the token's own projection)
+                    for (int j = 0; j + 1 < taps; ++j)
+                        st[(size_t)j * N + c] = j + 2 < taps ? st[(size_t)(j + 1) * N + c] : to_float(proj[(size_t)t * N + c]);
                 }
             }
             v[i] = acc;
@@ -105,8 +114,8 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
             }
         }
     }
-    // 4. where it goes
-    if (is_q) {
+    // 4. where it goes (keys and values of a long step stay in the row: a kernel that writes whole pieces of pages takes them from there)
+    if (is_q || !to_cache) {
         T* o = out + (size_t)t * N + c0;
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) {
@@ -141,11 +150,14 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
 // conv_w [(nh + 2 nkv) dh, taps] float (NULL: no convolution; one tap: a factor per channel, no state); state [slots, state_stride] float with the
 // convolution's rows at state_off; q_norm, k_norm [dh] float (NULL: no norm), the mean of squares over norm_width
 // elements (dh, or fewer when heads are padded with zeros); rotary_dim 0: no rotation.  write 0: only q is made.
-LI_EXPORT int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* conv_w, int taps, const float* state,
+// to_cache 0: keys and values go to their columns of `out` instead of the cache (li_rope_kv_write with rotary_dim 0 stores them).
+// shift: the caller promises that every sequence of the step has one token; the state then moves on in this launch
+// (with write 0 it does not move at all: the entry that writes the cache moves it).
+LI_EXPORT int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const float* conv_w, int taps, float* state,
                                    long long state_stride, long long state_off, const int* q_start, const int* seq_of_token, const int* slots,
                                    const float* q_norm, const float* k_norm, float eps, int norm_width, const int* positions, const float* denom,
                                    int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T, int nh, int nkv, int dh,
-                                   int page_size, int num_pages, int write, cudaStream_t stream) {
+                                   int page_size, int num_pages, int write, int shift, int to_cache, cudaStream_t stream) {
     LI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && dh > 0 && page_size > 0, "conv_norm_rope_kv: bad sizes");
     LI_REQUIRE(dh <= 32 * kPerLane, "conv_norm_rope_kv: head_dim %d is larger than %d", dh, 32 * kPerLane);
     LI_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= dh, "conv_norm_rope_kv: rotary_dim %d must be even and at most head_dim %d",
@@ -162,14 +174,25 @@ LI_EXPORT int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const
     const dim3 grid((unsigned)ceil_div_ll(total, kWarps));
     const size_t smem = (size_t)kWarps * dh * sizeof(float);
     cudaError_t e;
-    if (dtype == LI_F32)
-        e = li_launch_pdl(conv_norm_rope_kv_kernel<float>, grid, dim3(kWarps * 32), smem, stream, (const float*)proj, (float*)out, conv_w, taps,
-                          state, state_stride, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, positions, denom,
-                          rotary_dim, slot_mapping, (float*)kcache, (float*)vcache, (int)total, nh, nkv, dh, page_size, num_pages, write);
-    else
-        e = li_launch_pdl(conv_norm_rope_kv_kernel<bf16>, grid, dim3(kWarps * 32), smem, stream, (const bf16*)proj, (bf16*)out, conv_w, taps,
-                          state, state_stride, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, positions, denom,
-                          rotary_dim, slot_mapping, (bf16*)kcache, (bf16*)vcache, (int)total, nh, nkv, dh, page_size, num_pages, write);
+#define LI_CONV_LAUNCH(TT, TAPS_)                                                                                                             \
+    e = li_launch_pdl(conv_norm_rope_kv_kernel<TT, TAPS_>, grid, dim3(kWarps * 32), smem, stream, (const TT*)proj, (TT*)out, conv_w, taps, state, \
+                      state_stride, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, positions, denom, rotary_dim,      \
+                      slot_mapping, (TT*)kcache, (TT*)vcache, (int)total, nh, nkv, dh, page_size, num_pages, write, (shift && write) ? 1 : 0, to_cache)
+#define LI_CONV_TAPS(TT)                         \
+    switch (conv_w ? taps : 1) {                 \
+        case 1: LI_CONV_LAUNCH(TT, 1); break;    \
+        case 2: LI_CONV_LAUNCH(TT, 2); break;    \
+        case 3: LI_CONV_LAUNCH(TT, 3); break;    \
+        case 4: LI_CONV_LAUNCH(TT, 4); break;    \
+        default: LI_CONV_LAUNCH(TT, 0); break;   \
+    }
+    if (dtype == LI_F32) {
+        LI_CONV_TAPS(float)
+    } else {
+        LI_CONV_TAPS(bf16)
+    }
+#undef LI_CONV_TAPS
+#undef LI_CONV_LAUNCH
     if (e != cudaSuccess) return li_fail("conv_norm_rope_kv: launch failed: %s", cudaGetErrorString(e));
     return li_check_launch("conv_norm_rope_kv");
 }

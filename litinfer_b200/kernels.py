@@ -746,17 +746,45 @@ def gated_rmsnorm(y32: torch.Tensor, gate: torch.Tensor, gate_col: int, weight: 
 # norms on both sides of a sublayer, a vector per pass, norms of column ranges
 # --------------------------------------------------------------------------
 
-def norm_add_norm(x32: torch.Tensor, y: Optional[torch.Tensor], post: Optional[tuple], nxt: Optional[tuple], out: Optional[torch.Tensor],
+class RowSum:
+    """An activation [T, H] that stands for ``sum_k rows[place_of[t * top + k]]`` (times ``weights[t, k]`` if given): what a
+    mixture of experts leaves, until a kernel that consumes the sum takes it in (:func:`norm_add_norm`);
+    :meth:`materialize` adds the rows up with a kernel of its own (:func:`moe_combine`)."""
+
+    def __init__(self, rows: torch.Tensor, place_of: torch.Tensor, top: int, weights: Optional[torch.Tensor] = None) -> None:
+        self.rows, self.place_of, self.top, self.weights = rows, place_of, int(top), weights
+        self.shape = (place_of.numel() // self.top, rows.shape[1])
+        self.dtype = rows.dtype
+
+    def materialize(self) -> torch.Tensor:
+        y = torch.empty(self.shape, dtype=self.rows.dtype, device=self.rows.device)
+        moe_combine(self.rows, self.place_of, self.weights, self.top, y)
+        return y
+
+
+def norm_add_norm(x32: torch.Tensor, y, post: Optional[tuple], nxt: Optional[tuple], out: Optional[torch.Tensor],
                   rows: Optional[torch.Tensor] = None) -> None:
     """Per token: ``x32 += post(y)``, then ``out = nxt(x32)``.  A norm is a tuple ``(weight, centered, eps)``: centered takes
     the mean off and divides by the root of the variance (mean of squared deviations) + eps, not centered divides by the
     root of the mean of squares + eps; both multiply by the weight.  ``post`` None: ``x32 += y``; ``y`` None: nothing is
-    added; ``nxt`` None: no output.  ``rows`` (int32, only without ``y``): ``out[r] = nxt(x32[rows[r]])``."""
+    added; ``nxt`` None: no output.  ``rows`` (int32, only without ``y``): ``out[r] = nxt(x32[rows[r]])``.  ``y`` may be a
+    :class:`RowSum`: the sum is then taken inside this kernel, in float32."""
     n_src, H = x32.shape
     _need(x32, "residual stream", torch.float32)
     R = n_src if rows is None else rows.shape[0]
-    if y is not None:
+    places, top, y_weights = None, 0, None
+    if isinstance(y, RowSum):
+        if H > 8192:
+            y = y.materialize()
+        else:
+            places, top, y_weights, y = y.place_of, y.top, y.weights, y.rows
+            _need(y, "rows of the sublayer's output", None, (y.shape[0], H))
+            _need(places, "places of a token's rows", torch.int32, (n_src * top,))
+            if y_weights is not None:
+                _need(y_weights, "weights of a token's rows", torch.float32, (n_src, top))
+    if y is not None and places is None:
         _need(y, "sublayer output", None, (n_src, H))
+    if y is not None:
         if rows is not None:
             raise KernelError("norm_add_norm: gathered rows cannot take a sublayer's output")
     if rows is not None:
@@ -770,7 +798,8 @@ def norm_add_norm(x32: torch.Tensor, y: Optional[torch.Tensor], post: Optional[t
         _need(out, "normalised output", y.dtype if y is not None else None, (R, H))
     dt = _dt(y) if y is not None else _dt(out)
     _check(library().li_norm_add_norm(_p(x32), _p(y), _i(dt), _p(wp), _i(1 if cp else 0), _f(ep), _p(wn), _i(1 if cn else 0), _f(en),
-                                      _p(out if wn is not None else None), _p(rows), _i(R), _i(n_src), _i(H), _stream(x32)), "norm_add_norm")
+                                      _p(out if wn is not None else None), _p(rows), _i(R), _i(n_src), _i(H), _p(places), _i(top), _p(y_weights),
+                                      _stream(x32)), "norm_add_norm")
 
 
 def add_row(x32: torch.Tensor, row: torch.Tensor) -> None:
@@ -799,14 +828,17 @@ def conv_norm_rope_kv(proj: torch.Tensor, out: torch.Tensor, conv_w: Optional[to
                       q_start: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor, q_norm: Optional[torch.Tensor],
                       k_norm: Optional[torch.Tensor], eps: float, norm_width: int, positions: torch.Tensor,
                       denominators: Optional[torch.Tensor], rotary_dim: int, slot_mapping: torch.Tensor, k_cache: torch.Tensor,
-                      v_cache: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, write: bool = True) -> None:
+                      v_cache: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, write: bool = True, shift: bool = False,
+                      to_cache: bool = True) -> None:
     """What stands between a q|k|v product ``proj`` [T, (heads + 2 kv_heads) head_dim] and attention: a causal convolution
     per channel over the last ``taps`` projected rows (``conv_w`` float32 [channels, taps], the last column the token's own;
     rows before a portion come from ``state[slot, state_off:]`` as [taps - 1, channels], oldest first; one tap is a factor
     per channel and reads no state; None: no convolution), an RMS
     norm per query and key head (``q_norm``, ``k_norm`` [head_dim], the mean over ``norm_width`` elements; None: none), the
     rotation of the first ``rotary_dim`` elements of queries and keys; queries to the q columns of ``out``, keys and values
-    into the paged cache.  The state is not changed (:func:`conv_state_shift` moves it on)."""
+    into the paged cache.  The state is not changed (:func:`conv_state_shift` moves it on), unless ``shift``: the caller
+    promises that every sequence of the step has one token, and the state moves on in the same launch.  ``to_cache`` false:
+    keys and values go to their columns of ``out`` instead (:func:`rope_kv_write` with ``rotary_dim`` 0 stores them from there)."""
     T = proj.shape[0]
     N = (num_heads + 2 * num_kv_heads) * head_dim
     _need(proj, "q|k|v projection", None, (T, N))
@@ -841,7 +873,7 @@ def conv_norm_rope_kv(proj: torch.Tensor, out: torch.Tensor, conv_w: Optional[to
         _p(proj), _p(out), _i(_dt(proj)), _p(conv_w), _i(taps), st, stride, off, _p(q_start), _p(seq_of_token), _p(slots),
         _p(q_norm), _p(k_norm), _f(eps), _i(int(norm_width)), _p(positions), _p(denominators if rotary_dim else None), _i(rotary_dim),
         _p(slot_mapping), _p(k_cache), _p(v_cache), _i(T), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages),
-        _i(1 if write else 0), _stream(out)), "conv_norm_rope_kv")
+        _i(1 if write else 0), _i(1 if shift else 0), _i(1 if to_cache else 0), _stream(out)), "conv_norm_rope_kv")
 
 
 # --------------------------------------------------------------------------

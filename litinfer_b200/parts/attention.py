@@ -47,6 +47,7 @@ from .linear import FusedLinear, undefer
 @MIXERS.register("attention")
 class PagedAttention(Mixer):
     takes_deferred = True            # the q|k|v product applies the factor
+    CACHE_WRITE_APART = 64           # tokens of a step from which the kernel behind the product leaves the cache write to another
 
     def __init__(self, spec, prefix, dtype, device):
         super().__init__(spec, prefix, dtype, device)
@@ -191,11 +192,18 @@ class PagedAttention(Mixer):
             # projection; then convolution, norm per head, rotation and the cache write as one kernel; then the state moves on
             proj = self.qkv(h)
             qkv = torch.empty_like(proj)
+            # a step of single tokens: the convolution moves its state on itself
+            single = ctx.max_q_len == 1 and state is not None and state.writes and cache.writes
+            # a long step: keys and values go into the cache through the kernel that writes whole pieces of pages (the
+            # transposed values one element at a time are slow)
+            long_step = h.shape[0] >= self.CACHE_WRITE_APART
             K.conv_norm_rope_kv(proj, qkv, self.conv_weight, state.state if state is not None else None, 0, ctx.q_start, ctx.seq_of_token,
                                 ctx.state_slots, self.q_norm, self.k_norm, self.qk_norm_eps, self.qk_dim, ctx.positions,
                                 rot.denominators if rot else None, rot.rotary_dim if rot else 0, view.slot_mapping, cache.k, cache.v,
-                                self.num_heads, self.num_kv_heads, self.head_dim, cache.writes)
-            if state is not None and state.writes:
+                                self.num_heads, self.num_kv_heads, self.head_dim, cache.writes, shift=single, to_cache=not long_step)
+            if long_step and cache.writes:
+                K.rope_kv_write(qkv, ctx.positions, None, 0, view.slot_mapping, cache.k, cache.v, self.num_heads, self.num_kv_heads, self.head_dim, True)
+            if state is not None and state.writes and not single:
                 K.conv_state_shift(proj, 0, self.qkv_width, self.taps, state.state, 0, ctx.q_start, ctx.state_slots)
         else:
             h, row_scale = undefer(h, self.qkv.weight)

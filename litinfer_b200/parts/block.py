@@ -214,6 +214,7 @@ class SandwichBlock(Block):
             h = self._close(x32, y, self.mixer_post_norm, nxt)
             return x32, (Carry(normed=h) if h is not None else None)
         h = self._close(x32, y, self.mixer_post_norm, self.feed_forward_norm)
-        y = self.feed_forward.forward(h, ctx)
+        # (a mixture of experts hands its rows over as they are: the pass over the stream sums a token's rows itself)
+        y = self.feed_forward.forward_rows(h, ctx) if getattr(self.feed_forward, "produces_row_sums", False) else self.feed_forward.forward(h, ctx)
         h = self._close(x32, y, self.feed_forward_post_norm, nxt)
         return x32, (Carry(normed=h) if h is not None else None)

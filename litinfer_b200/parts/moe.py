@@ -10,7 +10,7 @@ How a step runs it: the router's product with a float32 result, the choice per t
 counting sort of the (token, choice) pairs by expert on the device (in a step of many tokens every expert's run starts
 at a multiple of 128 rows), one gather that builds the experts' input rows in sorted order (with the weight on them), a product per expert over its run of rows for gate|up and for down
 (``kernels.grouped_linear`` with the row offsets the sort left on the device), and a combine that sums a token's rows in
-the order of its choices.  Nothing comes back to the host, so the launches are the same whatever the routing, and a step
+the order of its choices (a kernel of its own, or part of the kernel that adds the result to the residual stream).  Nothing comes back to the host, so the launches are the same whatever the routing, and a step
 of single tokens can be captured.  A row's result does not depend on which rows share its expert.
 """
 
@@ -76,7 +76,14 @@ class RoutedExperts(FeedForward):
         self.gate_up = torch.stack(gu).contiguous()
         self.down = torch.stack(dn).contiguous()
 
+    # forward_rows: the experts' output rows and where each token's lie (kernels.RowSum), for a block whose next kernel takes
+    # the sum in (parts.block.SandwichBlock); forward: the sum itself
+    produces_row_sums = True
+
     def forward(self, h, ctx):
+        return self.forward_rows(h, ctx).materialize()
+
+    def forward_rows(self, h, ctx) -> "K.RowSum":
         T = h.shape[0]
         E, top, F = self.experts, self.top, self.intermediate
         dev = h.device
@@ -104,6 +111,4 @@ class RoutedExperts(FeedForward):
             K.grouped_linear(rows, self.gate_up, both, offsets, tile_group=tiles)
             K.swiglu(both, act)
         K.grouped_linear(act, self.down, rows, offsets, tile_group=tiles)
-        y = torch.empty((T, self.hidden), dtype=self.dtype, device=dev)
-        K.moe_combine(rows, place_of, None if on_input else weights, top, y)
-        return y
+        return K.RowSum(rows, place_of, top, None if on_input else weights)

@@ -236,6 +236,10 @@ def _norm_of(v, spec):
 
 
 def norm_add_norm(x32, y, post, nxt, out, rows=None):
+    if hasattr(y, "place_of"):                           # a sum of rows (kernels.RowSum), taken in float32
+        T, H = x32.shape
+        r = y.rows[y.place_of.long()].float().view(T, y.top, H)
+        y = (r * y.weights[:, :, None] if y.weights is not None else r).sum(1)
     if y is not None:
         x32.add_(_norm_of(y, post) if post is not None else y.float())
     if nxt is not None:
@@ -255,7 +259,13 @@ def rmsnorm_cols(x, col, n, width, weight, eps, out, col_a, col_b=-1):
 
 
 def conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, positions,
-                      denominators, rotary_dim, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim, write=True):
+                      denominators, rotary_dim, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim, write=True, shift=False, to_cache=True):
+    if shift and write and conv_w is not None and conv_w.shape[1] > 1:
+        # (the state moves on after the convolution has read it: taken care of at the end)
+        conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, positions,
+                          denominators, rotary_dim, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim, write, False, to_cache)
+        conv_state_shift(proj, 0, proj.shape[1], conv_w.shape[1], state, state_off, q_start, slots)
+        return
     T, N = proj.shape
     u = proj.float()
     if conv_w is not None:
@@ -292,6 +302,10 @@ def conv_norm_rope_kv(proj, out, conv_w, state, state_off, q_start, seq_of_token
         return
     k = shape(u[:, q_dim:q_dim + kv_dim].reshape(T, num_kv_heads, head_dim), k_norm).to(out.dtype)
     v = u[:, q_dim + kv_dim:].reshape(T, num_kv_heads, head_dim).to(out.dtype)
+    if not to_cache:
+        out[:, q_dim:q_dim + kv_dim] = k.reshape(T, kv_dim)
+        out[:, q_dim + kv_dim:] = v.reshape(T, kv_dim)
+        return
     page_size = k_cache.shape[2]
     page = (slot_mapping // page_size).long()
     off = (slot_mapping % page_size).long()

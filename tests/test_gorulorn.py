@@ -576,6 +576,18 @@ def test_norms_on_both_sides_of_a_sublayer_kernel(H, dtype):
         _close(xa, xb, "float32", "stream")
         if nxt:
             _close(oa, ob, dtype, "normalised")
+    # the sublayer's output as a sum of rows that lie elsewhere (a token's experts), with and without weights
+    top = 3
+    pool = torch.randn(T * top + 5, H).to(dev, dt)
+    place = torch.randperm(T * top + 5)[:T * top].to(torch.int32).to(dev)
+    wts = torch.rand(T, top).to(dev)
+    for weights in (None, wts):
+        xa, xb = x.clone(), x.clone()
+        oa, ob = (torch.empty(T, H, dtype=dt, device=dev) for _ in range(2))
+        K.norm_add_norm(xa, K.RowSum(pool, place, top, weights), (wp, True, 1e-5), (wn, True, 1e-5), oa)
+        R.norm_add_norm(xb, K.RowSum(pool, place, top, weights), (wp, True, 1e-5), (wn, True, 1e-5), ob)
+        _close(xa, xb, "float32", "stream (sum of rows)")
+        _close(oa, ob, dtype, "normalised (sum of rows)")
     oa, ob = (torch.empty(4, H, dtype=dt, device=dev) for _ in range(2))
     K.norm_add_norm(x, None, None, (wn, True, 1e-5), oa, rows=rows)
     R.norm_add_norm(x, None, None, (wn, True, 1e-5), ob, rows=rows)
@@ -632,6 +644,33 @@ def test_convolution_norm_rotation_and_cache_write_kernel(taps, rot, norm, dtype
         res.append((out[:, :nh * dh], kc, vc, st))
     for a, b, what in zip(res[0], res[1], ("queries", "keys", "values", "state")):
         _close(a, b, dtype, what)
+    # keys and values left in the row for another kernel to store
+    rows_out = []
+    for F in (K, R):
+        out = torch.zeros(T, N, dtype=dt, device=dev)
+        kc = torch.zeros(11, nkv, page, dh, dtype=dt, device=dev)
+        vc = torch.zeros(11, nkv, dh, page, dtype=dt, device=dev)
+        F.conv_norm_rope_kv(proj, out, conv, state.clone(), 7, i32(starts), i32(seq), i32(slots), qn, kn, 1e-5, dh, i32(pos), den, rot, slot_map, kc, vc, nh, nkv,
+                            dh, to_cache=False)
+        F.rope_kv_write(out, i32(pos), None, 0, slot_map, kc, vc, nh, nkv, dh)
+        rows_out.append((out, kc, vc))
+    for a, b, what in zip(rows_out[0], rows_out[1], ("rows", "keys", "values")):
+        _close(a, b, dtype, what + " (stored apart)")
+    _close(rows_out[0][1], res[0][1], dtype, "keys stored apart against stored at once")
+    _close(rows_out[0][2], res[0][2], dtype, "values stored apart against stored at once")
+    # a step of single tokens: the state moves on in the same launch
+    S = 4
+    res = []
+    for F in (K, R):
+        out = torch.zeros(S, N, dtype=dt, device=dev)
+        kc = torch.zeros(11, nkv, page, dh, dtype=dt, device=dev)
+        vc = torch.zeros(11, nkv, dh, page, dtype=dt, device=dev)
+        st = state.clone()
+        F.conv_norm_rope_kv(proj[:S].contiguous(), out, conv, st, 7, i32(list(range(S + 1))), i32(list(range(S))), i32(slots), qn, kn, 1e-5, dh,
+                            i32(first), den, rot, slot_map[:S].contiguous(), kc, vc, nh, nkv, dh, shift=True)
+        res.append((out[:, :nh * dh], kc, vc, st))
+    for a, b, what in zip(res[0], res[1], ("queries", "keys", "values", "state")):
+        _close(a, b, dtype, what + " (single tokens)")
 
 
 @pytest.mark.gpu
