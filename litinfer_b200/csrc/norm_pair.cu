@@ -68,11 +68,123 @@ __global__ void norm_add_norm_kernel(float* __restrict__ x, const T* __restrict_
     }
 }
 
-// The same with the row in registers: thread i holds elements i, i + blockDim, ... (up to kRegs of them), so the row of y
-// and the row of x are read once and every moment is taken from registers.  H <= kRegs * blockDim.
+// The same with the row in registers, so that the row of y and the row of x are read once and every moment is taken from
+// registers.  kVec (H a multiple of 8): a thread holds 8 neighbouring elements and moves them with 16-byte loads and
+// stores; else thread i holds elements i, i + blockDim, ... (up to kRegs of them).  H <= kRegs * blockDim.
 constexpr int kRegs = 8;
 
-template <typename T>
+template <bool kVec>
+__device__ __forceinline__ int reg_index(int k) { return kVec ? (int)threadIdx.x * kRegs + k : (int)threadIdx.x + k * (int)blockDim.x; }
+
+template <bool kVec>
+__device__ __forceinline__ void load_row(float (&v)[kRegs], const float* __restrict__ p, int H) {
+    if constexpr (kVec) {
+        const int i0 = threadIdx.x * kRegs;
+        if (i0 < H) {
+            const float4 a = *reinterpret_cast<const float4*>(p + i0), b = *reinterpret_cast<const float4*>(p + i0 + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int k = 0; k < kRegs; ++k) v[k] = 0.0f;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < kRegs; ++k) {
+            const int i = reg_index<false>(k);
+            v[k] = i < H ? p[i] : 0.0f;
+        }
+    }
+}
+
+template <bool kVec>
+__device__ __forceinline__ void load_row(float (&v)[kRegs], const bf16* __restrict__ p, int H) {
+    if constexpr (kVec) {
+        const int i0 = threadIdx.x * kRegs;
+        if (i0 < H) {
+            const uint4 a = *reinterpret_cast<const uint4*>(p + i0);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(h[k]);
+                v[2 * k] = f.x;
+                v[2 * k + 1] = f.y;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < kRegs; ++k) v[k] = 0.0f;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < kRegs; ++k) {
+            const int i = reg_index<false>(k);
+            v[k] = i < H ? __bfloat162float(p[i]) : 0.0f;
+        }
+    }
+}
+
+template <bool kVec>
+__device__ __forceinline__ void store_row(float* __restrict__ p, const float (&v)[kRegs], int H) {
+    if constexpr (kVec) {
+        const int i0 = threadIdx.x * kRegs;
+        if (i0 < H) {
+            *reinterpret_cast<float4*>(p + i0) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(p + i0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < kRegs; ++k) {
+            const int i = reg_index<false>(k);
+            if (i < H) p[i] = v[k];
+        }
+    }
+}
+
+template <bool kVec>
+__device__ __forceinline__ void store_row(bf16* __restrict__ p, const float (&v)[kRegs], int H) {
+    if constexpr (kVec) {
+        const int i0 = threadIdx.x * kRegs;
+        if (i0 < H) {
+            uint4 a;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&a);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+            *reinterpret_cast<uint4*>(p + i0) = a;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < kRegs; ++k) {
+            const int i = reg_index<false>(k);
+            if (i < H) p[i] = __float2bfloat16_rn(v[k]);
+        }
+    }
+}
+
+// (v - mean) * rinv * w for the thread's elements; mean 0 if not centered
+template <bool kVec>
+__device__ __forceinline__ void row_norm(float (&dst)[kRegs], const float (&v)[kRegs], const float* __restrict__ w, int centered, float eps, int H,
+                                         float* scratch) {
+    const float inv_h = 1.0f / (float)H;
+    float mean = 0.0f;
+    if (centered) {
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kRegs; ++k) s += v[k];
+        mean = block_sum(s, scratch) * inv_h;
+    }
+    float q = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kRegs; ++k) {
+        const float d = reg_index<kVec>(k) < H ? v[k] - mean : 0.0f;
+        q = fmaf(d, d, q);
+    }
+    const float rinv = 1.0f / sqrtf(block_sum(q, scratch) * inv_h + eps);
+    float wv[kRegs];
+    load_row<kVec>(wv, w, H);
+#pragma unroll
+    for (int k = 0; k < kRegs; ++k) dst[k] = (v[k] - mean) * rinv * wv[k];
+}
+
+template <typename T, bool kVec>
 __global__ void norm_add_norm_regs_kernel(float* __restrict__ x, const T* __restrict__ y, const float* __restrict__ w_post, int post_centered,
                                           float eps_post, const float* __restrict__ w_next, int next_centered, float eps_next,
                                           T* __restrict__ out, const int* __restrict__ rows, int n_src, int H,
@@ -87,13 +199,8 @@ __global__ void norm_add_norm_regs_kernel(float* __restrict__ x, const T* __rest
         if (src < 0 || src >= n_src) src = 0;
     }
     float* xr = x + (size_t)src * H;
-    const float inv_h = 1.0f / (float)H;
     float xv[kRegs];
-#pragma unroll
-    for (int k = 0; k < kRegs; ++k) {
-        const int i = threadIdx.x + k * blockDim.x;
-        xv[k] = i < H ? xr[i] : 0.0f;
-    }
+    load_row<kVec>(xv, xr, H);
     if (y) {
         float yv[kRegs];
         if (y_places) {
@@ -102,75 +209,30 @@ __global__ void norm_add_norm_regs_kernel(float* __restrict__ x, const T* __rest
 #pragma unroll
             for (int k = 0; k < kRegs; ++k) yv[k] = 0.0f;
             for (int j = 0; j < y_top; ++j) {
-                const T* yr = y + (size_t)y_places[(size_t)r * y_top + j] * H;
+                float part[kRegs];
+                load_row<kVec>(part, y + (size_t)y_places[(size_t)r * y_top + j] * H, H);
                 const float f = y_weights ? y_weights[(size_t)r * y_top + j] : 1.0f;
 #pragma unroll
-                for (int k = 0; k < kRegs; ++k) {
-                    const int i = threadIdx.x + k * blockDim.x;
-                    if (i < H) yv[k] = fmaf(f, to_float(yr[i]), yv[k]);
-                }
+                for (int k = 0; k < kRegs; ++k) yv[k] = fmaf(f, part[k], yv[k]);
             }
         } else {
-            const T* yr = y + (size_t)r * H;
-#pragma unroll
-            for (int k = 0; k < kRegs; ++k) {
-                const int i = threadIdx.x + k * blockDim.x;
-                yv[k] = i < H ? to_float(yr[i]) : 0.0f;
-            }
+            load_row<kVec>(yv, y + (size_t)r * H, H);
         }
         if (w_post) {
-            float mean = 0.0f;
-            if (post_centered) {
-                float s = 0.0f;
+            float nv[kRegs];
+            row_norm<kVec>(nv, yv, w_post, post_centered, eps_post, H, scratch);
 #pragma unroll
-                for (int k = 0; k < kRegs; ++k) s += yv[k];
-                mean = block_sum(s, scratch) * inv_h;
-            }
-            float q = 0.0f;
-#pragma unroll
-            for (int k = 0; k < kRegs; ++k) {
-                const int i = threadIdx.x + k * blockDim.x;
-                const float d = i < H ? yv[k] - mean : 0.0f;
-                q = fmaf(d, d, q);
-            }
-            const float rinv = 1.0f / sqrtf(block_sum(q, scratch) * inv_h + eps_post);
-#pragma unroll
-            for (int k = 0; k < kRegs; ++k) {
-                const int i = threadIdx.x + k * blockDim.x;
-                if (i < H) xv[k] += (yv[k] - mean) * rinv * w_post[i];
-            }
+            for (int k = 0; k < kRegs; ++k) xv[k] += nv[k];
         } else {
 #pragma unroll
             for (int k = 0; k < kRegs; ++k) xv[k] += yv[k];
         }
-#pragma unroll
-        for (int k = 0; k < kRegs; ++k) {
-            const int i = threadIdx.x + k * blockDim.x;
-            if (i < H) xr[i] = xv[k];
-        }
+        store_row<kVec>(xr, xv, H);
     }
     if (w_next) {
-        float mean = 0.0f;
-        if (next_centered) {
-            float s = 0.0f;
-#pragma unroll
-            for (int k = 0; k < kRegs; ++k) s += xv[k];
-            mean = block_sum(s, scratch) * inv_h;
-        }
-        float q = 0.0f;
-#pragma unroll
-        for (int k = 0; k < kRegs; ++k) {
-            const int i = threadIdx.x + k * blockDim.x;
-            const float d = i < H ? xv[k] - mean : 0.0f;
-            q = fmaf(d, d, q);
-        }
-        const float rinv = 1.0f / sqrtf(block_sum(q, scratch) * inv_h + eps_next);
-        T* o = out + (size_t)r * H;
-#pragma unroll
-        for (int k = 0; k < kRegs; ++k) {
-            const int i = threadIdx.x + k * blockDim.x;
-            if (i < H) o[i] = from_float<T>((xv[k] - mean) * rinv * w_next[i]);
-        }
+        float nv[kRegs];
+        row_norm<kVec>(nv, xv, w_next, next_centered, eps_next, H, scratch);
+        store_row<kVec>(out + (size_t)r * H, nv, H);
     }
 }
 
@@ -223,12 +285,20 @@ LI_EXPORT int li_norm_add_norm(float* x, const void* y, int dtype, const float* 
         // the row in registers: as few threads as hold it, a multiple of 32, at least 64
         int threads = ((ceil_div(H, kRegs) + 31) / 32) * 32;
         if (threads < 64) threads = 64;
-        if (dtype == LI_F32)
-            e = li_launch_pdl(norm_add_norm_regs_kernel<float>, dim3(R), dim3(threads), 0, stream, x, (const float*)y, w_post, post_centered, eps_post,
-                              w_next, next_centered, eps_next, (float*)out, rows, n_src, H, y_places, y_top, y_weights);
-        else
-            e = li_launch_pdl(norm_add_norm_regs_kernel<bf16>, dim3(R), dim3(threads), 0, stream, x, (const bf16*)y, w_post, post_centered, eps_post,
-                              w_next, next_centered, eps_next, (bf16*)out, rows, n_src, H, y_places, y_top, y_weights);
+        // 16-byte moves where every row starts on such a boundary
+        const bool vec = H % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
+                         ((uintptr_t)w_post % 16) == 0 && ((uintptr_t)w_next % 16) == 0;
+#define LI_NORM_LAUNCH(TT, VEC)                                                                                                                  \
+    e = li_launch_pdl(norm_add_norm_regs_kernel<TT, VEC>, dim3(R), dim3(threads), 0, stream, x, (const TT*)y, w_post, post_centered, eps_post, w_next, \
+                      next_centered, eps_next, (TT*)out, rows, n_src, H, y_places, y_top, y_weights)
+        if (dtype == LI_F32) {
+            if (vec) LI_NORM_LAUNCH(float, true);
+            else LI_NORM_LAUNCH(float, false);
+        } else {
+            if (vec) LI_NORM_LAUNCH(bf16, true);
+            else LI_NORM_LAUNCH(bf16, false);
+        }
+#undef LI_NORM_LAUNCH
         if (e != cudaSuccess) return li_fail("norm_add_norm: launch failed: %s", cudaGetErrorString(e));
         return li_check_launch("norm_add_norm");
     }

@@ -20,7 +20,9 @@ constexpr int kWarps = 4;
 constexpr int kPerLane = 16;        // head_dim <= 512
 
 // TAPS: the taps at compile time (their loads are then all in flight at once), or 0: any number, at run time.
-template <typename T, int TAPS>
+// PER: elements of a head a lane holds (4: heads of up to 128; 16: up to 512); the loops over them are unrolled, and the
+// short form has a third of the instructions and registers of the long one.
+template <typename T, int TAPS, int PER>
 __global__ void __launch_bounds__(kWarps * 32)
 conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const float* __restrict__ conv_w, int taps_rt,
                          float* __restrict__ state, long long state_stride, long long state_off, const int* __restrict__ q_start,
@@ -42,7 +44,7 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
     if (!is_q && !write) return;
     const int c0 = head * dh;
     const int per = (dh + 31) >> 5;
-    float v[kPerLane];
+    float v[PER];
     // 1. the convolution (or the plain value)
     if (conv_w != nullptr) {
         const int s = seq_of_token[t];
@@ -50,7 +52,7 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
         const int li = t - q0;
         float* st = taps > 1 ? state + (size_t)slots[s] * state_stride + state_off : nullptr;      // one tap reads no older row
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int d = lane + 32 * i;
             float acc = 0.0f;
             if (i < per && d < dh) {
@@ -72,7 +74,7 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
         }
     } else {
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int d = lane + 32 * i;
             v[i] = (i < per && d < dh) ? to_float(proj[(size_t)t * N + c0 + d]) : 0.0f;
         }
@@ -82,11 +84,11 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
     if (nw) {
         float q = 0.0f;
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) q = fmaf(v[i], v[i], q);
+        for (int i = 0; i < PER; ++i) q = fmaf(v[i], v[i], q);
         q = warp_sum(q);
         const float rinv = 1.0f / sqrtf(q / (float)norm_width + eps);
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int d = lane + 32 * i;
             if (i < per && d < dh) v[i] = v[i] * rinv * nw[d];
         }
@@ -95,7 +97,7 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
     if (rotary_dim > 0 && (is_q || is_k)) {
         float* sh = smem + (size_t)warp_in_block * dh;
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int d = lane + 32 * i;
             if (i < per && d < dh) sh[d] = v[i];
         }
@@ -103,7 +105,7 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
         const int half = rotary_dim >> 1;
         const float pos = (float)positions[t];
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int d = lane + 32 * i;
             if (i < per && d < rotary_dim) {
                 const int j = d < half ? d : d - half;
@@ -118,7 +120,7 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
     if (is_q || !to_cache) {
         T* o = out + (size_t)t * N + c0;
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int d = lane + 32 * i;
             if (i < per && d < dh) o[d] = from_float<T>(v[i]);
         }
@@ -130,14 +132,14 @@ conv_norm_rope_kv_kernel(const T* __restrict__ proj, T* __restrict__ out, const 
     if (is_k) {
         T* dst = kcache + (((size_t)page * nkv + (head - nh)) * page_size + off) * dh;
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int d = lane + 32 * i;
             if (i < per && d < dh) dst[d] = from_float<T>(v[i]);
         }
     } else {
         T* dst = vcache + ((size_t)page * nkv + (head - nh - nkv)) * dh * page_size + off;
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int d = lane + 32 * i;
             if (i < per && d < dh) dst[(size_t)d * page_size] = from_float<T>(v[i]);
         }
@@ -175,7 +177,7 @@ LI_EXPORT int li_conv_norm_rope_kv(const void* proj, void* out, int dtype, const
     const size_t smem = (size_t)kWarps * dh * sizeof(float);
     cudaError_t e;
 #define LI_CONV_LAUNCH(TT, TAPS_)                                                                                                             \
-    e = li_launch_pdl(conv_norm_rope_kv_kernel<TT, TAPS_>, grid, dim3(kWarps * 32), smem, stream, (const TT*)proj, (TT*)out, conv_w, taps, state, \
+    e = li_launch_pdl(dh <= 128 ? conv_norm_rope_kv_kernel<TT, TAPS_, 4> : conv_norm_rope_kv_kernel<TT, TAPS_, kPerLane>, grid, dim3(kWarps * 32), smem, stream, (const TT*)proj, (TT*)out, conv_w, taps, state, \
                       state_stride, state_off, q_start, seq_of_token, slots, q_norm, k_norm, eps, norm_width, positions, denom, rotary_dim,      \
                       slot_mapping, (TT*)kcache, (TT*)vcache, (int)total, nh, nkv, dh, page_size, num_pages, write, (shift && write) ? 1 : 0, to_cache)
 #define LI_CONV_TAPS(TT)                         \

@@ -556,7 +556,7 @@ def _close(a, b, dtype, what):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H", [48, 1000, 4096])
+@pytest.mark.parametrize("H", [48, 100, 1000, 4096])
 def test_norms_on_both_sides_of_a_sublayer_kernel(H, dtype):
     from litinfer_b200 import kernels as K
     import kernel_refs as R
