@@ -71,7 +71,8 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
                             int max_blocks, const int* __restrict__ q_start, const int* __restrict__ ctx_lens, int nh, int nkv,
                             int page_size, int num_pages, float scale, int window, int skip_single, int* __restrict__ error_flag, int trace,
-                            const int* __restrict__ units, float* __restrict__ partial, unsigned* __restrict__ counters) {
+                            const int* __restrict__ units, float* __restrict__ partial, unsigned* __restrict__ counters,
+                            const float* __restrict__ sinks) {
     extern __shared__ unsigned char smem_raw[];
     Smem<DH>& sm = *reinterpret_cast<Smem<DH>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // the tiles want 1024-byte alignment; with head_dim 128 there is not a whole kilobyte to spare for it
@@ -388,6 +389,7 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
             if (ok) l = sm.mx[jx & 1][0][r] + sm.mx[jx & 1][1][r];
         }
         bool store = valid;
+        float m_ref = m;                                          // the maximum that o and l stand against when they are divided
         if (parts > 1) {                                          // the same for the whole CTA; every softmax thread takes part, failed or not
             // Shared tile of tokens: this CTA's output (unnormalised, against its maximum m), m and the sum l go to the
             // workspace, [column][row] so that a warp writes consecutive words.  The CTA that arrives last adds all parts
@@ -417,6 +419,7 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
                 float m_all = -INFINITY;
                 for (int q = 0; q < parts; ++q) m_all = fmaxf(m_all, __ldcg(first + q * stride + DH * kRows + r));
                 const float ref = (m_all == -INFINITY) ? 0.0f : m_all;
+                m_ref = m_all;
 #pragma unroll
                 for (int d = 0; d < HD; ++d) o[d] = 0.0f;
                 l = 0.0f;
@@ -435,6 +438,8 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
         if (!ok) {
             if (lane == 0) atomicExch(error_flag, 13);
         } else if (store) {
+            // a sink: exp(sinks[h]) joins the denominator once (it has no key and no value); the maxima are in base-2 units
+            if (sinks != nullptr && m_ref != -INFINITY) l += exp2f(sinks[h] * 1.4426950408889634f - m_ref);
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             bf16* dst = out + ((size_t)(tok0 + cta_i0 + r) * nh + h) * DH + half * HD;
 #pragma unroll
@@ -494,7 +499,7 @@ SplitSpace& split_space() {
 template <int DH>
 int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks, const int* q_start,
            const int* ctx_lens, int T, int S, int nh, int nkv, int page_size, int num_pages, float scale, int window, int max_q_len,
-           int skip_single, const int* units, int unit_slots, cudaStream_t stream) {
+           int skip_single, const int* units, int unit_slots, const float* sinks, cudaStream_t stream) {
     EncodeTiledFn encode = nullptr;
     int *err_host = nullptr, *err_dev = nullptr;
     if (int rc = setup(&encode, &err_host, &err_dev)) return rc;
@@ -529,7 +534,7 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     static const int trace = getenv("LITINFER_B200_ATTN_TRACE") ? 1 : 0;
     li_launch_pdl(prefill_attention_tc_kernel<DH>, grid, dim3(kThreads), smem, stream, (const bf16*)qkv, row_elems, map_k, map_v, (bf16*)out, block_table, max_blocks,
                   q_start, ctx_lens, nh, nkv, page_size, num_pages, scale, window, skip_single, err_dev, trace, units, partial,
-                  space.counters);
+                  space.counters, sinks);
     return li_check_launch("attention (tcgen05)");
 }
 
@@ -542,13 +547,14 @@ bool li_attention_tcgen05_accepts(const void* qkv, const void* kcache, const voi
 
 int li_attention_tcgen05(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
-                         float scale, int window, int max_q_len, int skip_single, const int* units, int unit_slots, cudaStream_t stream) {
+                         float scale, int window, int max_q_len, int skip_single, const int* units, int unit_slots, const float* sinks,
+                         cudaStream_t stream) {
     LI_REQUIRE(li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size),
                "attention (tcgen05): refuses heads=%d/%d head_dim=%d page=%d (head_dim 64 or 128, pages a multiple of 16)", nh, nkv, dh, page_size);
     LI_REQUIRE(scale > 0.0f, "attention (tcgen05): the scale must be positive");
     if (dh == 64)
         return launch<64>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, page_size, num_pages, scale,
-                          window, max_q_len, skip_single, units, unit_slots, stream);
+                          window, max_q_len, skip_single, units, unit_slots, sinks, stream);
     return launch<128>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, page_size, num_pages, scale,
-                       window, max_q_len, skip_single, units, unit_slots, stream);
+                       window, max_q_len, skip_single, units, unit_slots, sinks, stream);
 }

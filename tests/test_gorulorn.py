@@ -290,12 +290,12 @@ def test_long_decoding_from_captured_steps(dtype, folders):
 # the window's edges, the kept first keys and the sink, with one key made to stand out
 # --------------------------------------------------------------------------
 
-def _attention_case(K, dev, dtype, window, keep, ctx, q_len, page_size, hot_key, sinks=None, implementation=None, copies=1):
+def _attention_case(K, dev, dtype, window, keep, ctx, q_len, page_size, hot_key, sinks=None, implementation=None, copies=1, dh=32):
     """One sequence of ``ctx`` keys whose last ``q_len`` tokens are this step's.  Keys and queries are small noise, except
     that every query has a large component along one key: the key ``hot_key`` positions behind it (an int), or the key
     at an absolute position (``("at", j)``); that key's value is a marker.  Returns the kernel's output and the operands."""
     torch.manual_seed(ctx * 31 + q_len)
-    nh, nkv, dh = 4, 2, 32
+    nh, nkv = 4, 2
     T, pages = q_len, -(-ctx // page_size)
     dt = torch.float32 if dtype == "float32" else torch.bfloat16
     k = 0.05 * torch.randn(ctx, nkv, dh)
@@ -323,6 +323,12 @@ def _attention_case(K, dev, dtype, window, keep, ctx, q_len, page_size, hot_key,
                 positions=i32(list(range(ctx - T, ctx)) * S), num_heads=nh, num_kv_heads=nkv, head_dim=dh, scale=1.0, window=window,
                 max_q_len=T, max_ctx_len=ctx)
     out = torch.empty(S * T, nh * dh, dtype=dt, device=dev)
+    if implementation == "prefill_tcgen05":
+        # with the work list the engine makes: few tiles of tokens behind a long context have their keys shared out among CTAs
+        from litinfer_b200.engine.batch import attention_units
+
+        units = attention_units([T], [ctx], work_budget=148 // nh)
+        args.update(units=torch.from_numpy(units).to(dev), unit_slots=(int(units[0]), int(units[1])))
     K.paged_attention(qkv.repeat(S, 1).to(dev, dt).contiguous(), out, **args, keep_first=keep, sinks=sinks.to(dev) if sinks is not None else None,
                       implementation=implementation)
     out = out.float().cpu()
@@ -399,21 +405,28 @@ def test_the_sink_takes_its_share_of_the_softmax(q_len, dtype, device, request):
     ("decode", 1, 700, 1),             # a unit of 256 keys per CTA, merged by the last one
     ("decode", 1, 700, 80),            # many sequences: a CTA walks the whole context
     ("decode", 1, 3000, 10),           # units of several rounds
-    ("prefill", 7, 700, 1), ("prefill", 130, 700, 1), ("prefill", 200, 333, 1)])
+    ("prefill", 7, 700, 1), ("prefill", 130, 700, 1), ("prefill", 200, 333, 1),
+    ("prefill_tcgen05", 130, 700, 1), ("prefill_tcgen05", 300, 333, 1), ("prefill_tcgen05", 64, 3000, 1)])      # (the sink only: heads of 64)
 def test_each_attention_kernel_alone_keeps_the_first_keys_and_takes_the_sink(implementation, q_len, ctx, copies):
     """Kept first keys (more of them than a tile of keys holds) and the sink in each bfloat16 attention kernel by itself,
     over a context of several pages, tiles and split units, with the hot key at every edge."""
     from litinfer_b200 import kernels as K
 
     dev, window, keep = torch.device("cuda:0"), 300, 70
+    dh = 32
+    if implementation == "prefill_tcgen05":
+        keep, dh = 0, 64                                            # the tcgen05 tiles take the sink, not the kept keys
     rnd = lambda x: x.to(torch.bfloat16).float()
     sinks = torch.tensor([0.5, 36.0, -3.0, 2.0])
     for hot, seen in ((window - 1, True), (window, ctx - 1 - window < keep), (5, True), (("at", 0), True), (("at", keep - 1), True), (("at", keep), ctx - 1 - keep < window),
                       (("at", 64), True), (("at", 63), True)):
-        out, (q, k, v) = _attention_case(K, dev, "bfloat16", window, keep, ctx, q_len, 16, hot, sinks=sinks, implementation=implementation, copies=copies)
+        if isinstance(hot, tuple) and keep == 0:
+            seen = ctx - 1 - hot[1] < window
+        out, (q, k, v) = _attention_case(K, dev, "bfloat16", window, keep, ctx, q_len, 16, hot, sinks=sinks, implementation=implementation, copies=copies,
+                                         dh=dh)
         ref = _plain_attention(rnd(q), rnd(k), rnd(v), window, keep, sinks)
         assert (out - ref).abs().max() <= 0.03 * ref.abs().max(), f"{implementation}: ctx {ctx}, {q_len} tokens, hot key {hot}"
-        last = out[-1].view(4, 32)[0, 0].abs()                      # head 0: its sink is negligible
+        last = out[-1].view(4, dh)[0, 0].abs()                      # head 0: its sink is negligible
         assert (last > 1.0) == seen, f"{implementation}: ctx {ctx}, {q_len} tokens: key {hot} {'is' if seen else 'is not'} seen"
 
 
