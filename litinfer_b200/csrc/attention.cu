@@ -32,7 +32,7 @@ bool li_attention_tcgen05_accepts(const void* qkv, const void* kcache, const voi
 int li_attention_tcgen05(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
                          float scale, int window, int max_q_len, int skip_single, const int* units, int unit_slots, const float* sinks,
-                         cudaStream_t stream);
+                         int keep_first, cudaStream_t stream);
 
 static int validate(int T, int S, int nh, int nkv, int dh, int page_size, int window) {
     LI_REQUIRE(T >= 0 && S > 0, "attention: bad batch T=%d S=%d", T, S);
@@ -51,10 +51,10 @@ static int attention_portions(const void* qkv, void* out, const void* kcache, co
                               int slots_portions, int slots_all, float softcap, const float* slopes, const void* gate, int keep_first,
                               const float* sinks, bool* done, cudaStream_t stream) {
     *done = false;
-    // changed scores or outputs (a cap, a distance penalty, a gate per head, kept first keys behind the window): the
-    // mma.sync tiles and the decode kernel take them, the tcgen05 tiles do not
-    // (a sink only changes the denominator at the end: the tcgen05 tiles take it)
-    const bool changed = softcap > 0.0f || slopes != nullptr || gate != nullptr || keep_first > 0;
+    // changed scores or outputs (a cap, a distance penalty, a gate per head): the mma.sync tiles and the decode kernel take
+    // them, the tcgen05 tiles do not
+    // (a sink only changes the denominator at the end, kept first keys are a few more key tiles: the tcgen05 tiles take both)
+    const bool changed = softcap > 0.0f || slopes != nullptr || gate != nullptr;
     const bool tc = !changed && max_q_len >= 64 && scale > 0.0f && li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size);
     if (!tc && scale <= 0.0f) return 0;
     if (!tc && !li_attention_prefill_accepts(nh, nkv, dh, page_size)) return 0;
@@ -69,7 +69,7 @@ static int attention_portions(const void* qkv, void* out, const void* kcache, co
     *done = true;
     if (tc)
         return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
-                                    num_pages, scale, window, max_q_len, split, units, split ? slots_portions : slots_all, sinks, stream);
+                                    num_pages, scale, window, max_q_len, split, units, split ? slots_portions : slots_all, sinks, keep_first, stream);
     return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
                                 num_pages, scale, window, max_q_len, split, softcap, slopes, gate, keep_first, sinks, stream);
 }
@@ -119,8 +119,7 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
     if (which == 0)
         return li_attention_generic(qkv, out, kcache, vcache, dtype, block_table, max_blocks, seq_of_token, positions, T, nh, nkv,
                                     dh, page_size, num_pages, scale, window, softcap, slopes, gate, keep_first, sinks, stream);
-    LI_REQUIRE(which != 3 || (softcap <= 0.0f && slopes == nullptr && gate == nullptr && keep_first == 0),
-               "attention: the tcgen05 kernel takes no cap, slopes, gate or kept first keys");
+    LI_REQUIRE(which != 3 || (softcap <= 0.0f && slopes == nullptr && gate == nullptr), "attention: the tcgen05 kernel takes no cap, slopes or gate");
     LI_REQUIRE(dtype == LI_BF16, "attention: implementation %d takes bfloat16 only", which);
     if (which == 1) {
         LI_REQUIRE(max_q_len == 1 && T == S, "attention: the decode kernel takes one token per sequence");
@@ -143,7 +142,7 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
             return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
                                         num_pages, scale, window, max_q_len, split, softcap, slopes, gate, keep_first, sinks, stream);
         return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
-                                    num_pages, scale, window, max_q_len, split, units, split ? slots_portions : slots_all, sinks, stream);
+                                    num_pages, scale, window, max_q_len, split, units, split ? slots_portions : slots_all, sinks, keep_first, stream);
     }
     return li_fail("attention: unknown implementation %d", which);
 }

@@ -19,7 +19,8 @@
 //              buffer.  O stays in tensor memory; it is scaled down only when a row's maximum has grown by more
 //              than 2^8 (see kLazy).  S of tile j + 1 is issued before P V of tile j.
 // Keys and values of the portion itself are already in the cache (the rope kernel ran before).  Token i of a
-// portion of n tokens in a context of c sits at position p = c - n + i and sees keys max(0, p - window + 1) .. p.
+// portion of n tokens in a context of c sits at position p = c - n + i and sees keys max(0, p - window + 1) .. p (and,
+// with a window, the sequence's first keep_first keys behind it).
 // Keys of a tile that lie past the context are read from whatever page the table names (page 0 if none) and get
 // probability zero; the cache holds finite numbers only.
 //
@@ -72,7 +73,7 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
                             int max_blocks, const int* __restrict__ q_start, const int* __restrict__ ctx_lens, int nh, int nkv,
                             int page_size, int num_pages, float scale, int window, int skip_single, int* __restrict__ error_flag, int trace,
                             const int* __restrict__ units, float* __restrict__ partial, unsigned* __restrict__ counters,
-                            const float* __restrict__ sinks) {
+                            const float* __restrict__ sinks, int keep_first) {
     extern __shared__ unsigned char smem_raw[];
     Smem<DH>& sm = *reinterpret_cast<Smem<DH>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // the tiles want 1024-byte alignment; with head_dim 128 there is not a whole kilobyte to spare for it
@@ -109,17 +110,26 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
     // The key tiles of this tile of tokens.  When the step has so few tiles of tokens that multiprocessors would stand idle,
     // the work list shares them out among several CTAs (entries with parts > 1), at least kPartTiles each, and the last
     // CTA to finish adds the partial results up.  The workspace has room for one partial result per multiprocessor.
-    const int tiles_all = p_last / kKeys - key_lo / kKeys + 1;
+    // With a window, the first keep_first keys of the sequence stay visible behind it: the tiles that hold them and lie
+    // before the window's first tile are walked first (entries 0 .. kept_tiles - 1 of the tile's list), then the window's.
+    const int win_first = key_lo / kKeys;
+    const int kept_tiles = (window > 0 && keep_first > 0) ? min((keep_first + kKeys - 1) / kKeys, win_first) : 0;
+    const int keep = window > 0 ? keep_first : 0;
+    const int tiles_all = p_last / kKeys - win_first + 1 + kept_tiles;
     int parts = min(parts_asked, (tiles_all + kPartTiles - 1) / kPartTiles);
     if ((first_entry + parts_asked) * nh > kMultiprocessors) parts = 1;
     if (part >= parts) return;
-    const int kt_first = key_lo / kKeys + (int)((long long)part * tiles_all / parts);
-    const int ntiles = key_lo / kKeys + (int)((long long)(part + 1) * tiles_all / parts) - kt_first;
+    const int list_first = (int)((long long)part * tiles_all / parts);
+    const int ntiles = (int)((long long)(part + 1) * tiles_all / parts) - list_first;
+    auto tile_of = [&](int j) {                                  // the key tile behind entry j of this CTA's share of the list
+        const int e = list_first + j;
+        return e < kept_tiles ? e : win_first + (e - kept_tiles);
+    };
     // the page of each 16-key block of a tile, for the lanes of the loading warps; the first tile's as early as possible
     // (the table and the lengths were written before the step's first kernel started, so they may be read before pdl_wait)
     const int* bt = block_table + (size_t)s * max_blocks;
     auto look_up = [&](int j, int& page, int& off) {
-        const int key = (kt_first + j) * kKeys + (lane & 7) * 16;
+        const int key = tile_of(j) * kKeys + (lane & 7) * 16;
         const int idx = key / page_size;
         page = (j < ntiles && key < ctx && idx < max_blocks) ? bt[idx] : 0;
         if (page < 0 || page >= num_pages) page = 0;
@@ -288,7 +298,7 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         mbar_arrive(&sm.q_full);
         for (int j = 0; j < ntiles && ok; ++j) {
-            const int key0 = (kt_first + j) * kKeys + half * HK;
+            const int key0 = tile_of(j) * kKeys + half * HK;
             if (lane == 0 && quarter == 0) stamp(2 + half, 0, j);
             ok = mbar_wait(&sm.s_full[j & 1], (j >> 1) & 1);
             if (!ok) break;
@@ -297,11 +307,11 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
             // this thread's 64 scores of the tile, read once and kept for both passes; a key the row does not see reads -inf
             float v[HK];
             tmem_ld_32x64(tmem_s + 128 * (j & 1) + lane_addr + half * HK, v);
-            const bool whole = key0 >= lo && key0 + HK - 1 <= p;
+            const bool whole = (key0 >= lo || key0 + HK <= keep) && key0 + HK - 1 <= p;
             if (!whole) {
 #pragma unroll
                 for (int i = 0; i < HK; ++i)
-                    if (key0 + i < lo || key0 + i > p) v[i] = -INFINITY;
+                    if ((key0 + i < lo && key0 + i >= keep) || key0 + i > p) v[i] = -INFINITY;
             }
             // the row's maximum over the tile: this half's, then the other thread's through shared memory
             float mine = -INFINITY;
@@ -499,7 +509,7 @@ SplitSpace& split_space() {
 template <int DH>
 int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks, const int* q_start,
            const int* ctx_lens, int T, int S, int nh, int nkv, int page_size, int num_pages, float scale, int window, int max_q_len,
-           int skip_single, const int* units, int unit_slots, const float* sinks, cudaStream_t stream) {
+           int skip_single, const int* units, int unit_slots, const float* sinks, int keep_first, cudaStream_t stream) {
     EncodeTiledFn encode = nullptr;
     int *err_host = nullptr, *err_dev = nullptr;
     if (int rc = setup(&encode, &err_host, &err_dev)) return rc;
@@ -534,7 +544,7 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     static const int trace = getenv("LITINFER_B200_ATTN_TRACE") ? 1 : 0;
     li_launch_pdl(prefill_attention_tc_kernel<DH>, grid, dim3(kThreads), smem, stream, (const bf16*)qkv, row_elems, map_k, map_v, (bf16*)out, block_table, max_blocks,
                   q_start, ctx_lens, nh, nkv, page_size, num_pages, scale, window, skip_single, err_dev, trace, units, partial,
-                  space.counters, sinks);
+                  space.counters, sinks, keep_first);
     return li_check_launch("attention (tcgen05)");
 }
 
@@ -548,13 +558,13 @@ bool li_attention_tcgen05_accepts(const void* qkv, const void* kcache, const voi
 int li_attention_tcgen05(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
                          float scale, int window, int max_q_len, int skip_single, const int* units, int unit_slots, const float* sinks,
-                         cudaStream_t stream) {
+                         int keep_first, cudaStream_t stream) {
     LI_REQUIRE(li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size),
                "attention (tcgen05): refuses heads=%d/%d head_dim=%d page=%d (head_dim 64 or 128, pages a multiple of 16)", nh, nkv, dh, page_size);
     LI_REQUIRE(scale > 0.0f, "attention (tcgen05): the scale must be positive");
     if (dh == 64)
         return launch<64>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, page_size, num_pages, scale,
-                          window, max_q_len, skip_single, units, unit_slots, sinks, stream);
+                          window, max_q_len, skip_single, units, unit_slots, sinks, keep_first, stream);
     return launch<128>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, page_size, num_pages, scale,
-                       window, max_q_len, skip_single, units, unit_slots, sinks, stream);
+                       window, max_q_len, skip_single, units, unit_slots, sinks, keep_first, stream);
 }

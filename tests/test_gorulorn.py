@@ -406,7 +406,7 @@ def test_the_sink_takes_its_share_of_the_softmax(q_len, dtype, device, request):
     ("decode", 1, 700, 80),            # many sequences: a CTA walks the whole context
     ("decode", 1, 3000, 10),           # units of several rounds
     ("prefill", 7, 700, 1), ("prefill", 130, 700, 1), ("prefill", 200, 333, 1),
-    ("prefill_tcgen05", 130, 700, 1), ("prefill_tcgen05", 300, 333, 1), ("prefill_tcgen05", 64, 3000, 1)])      # (the sink only: heads of 64)
+    ("prefill_tcgen05", 130, 700, 1), ("prefill_tcgen05", 300, 333, 1), ("prefill_tcgen05", 64, 3000, 1), ("prefill_tcgen05", 520, 1500, 1)])
 def test_each_attention_kernel_alone_keeps_the_first_keys_and_takes_the_sink(implementation, q_len, ctx, copies):
     """Kept first keys (more of them than a tile of keys holds) and the sink in each bfloat16 attention kernel by itself,
     over a context of several pages, tiles and split units, with the hot key at every edge."""
@@ -415,7 +415,7 @@ def test_each_attention_kernel_alone_keeps_the_first_keys_and_takes_the_sink(imp
     dev, window, keep = torch.device("cuda:0"), 300, 70
     dh = 32
     if implementation == "prefill_tcgen05":
-        keep, dh = 0, 64                                            # the tcgen05 tiles take the sink, not the kept keys
+        dh = 64                                                     # (heads of 64 or 128)
     rnd = lambda x: x.to(torch.bfloat16).float()
     sinks = torch.tensor([0.5, 36.0, -3.0, 2.0])
     for hot, seen in ((window - 1, True), (window, ctx - 1 - window < keep), (5, True), (("at", 0), True), (("at", keep - 1), True), (("at", keep), ctx - 1 - keep < window),
