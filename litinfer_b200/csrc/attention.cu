@@ -11,6 +11,10 @@
 //                                       single token as a portion of length one would occupy a whole tile of 64 or 128
 //                                       query rows for each head and read its keys once per query head.
 //   sizes those refuse               -> general kernel
+//
+// Every kernel takes a sink in the denominator and, with a window, the kept first keys.  A cap on the scores, a penalty
+// linear in the distance and a gate per head are forms of the general kernel, the mma.sync tiles and the decode kernel; a
+// step that asks for one of them does not go to the tcgen05 tiles.
 #include "common.cuh"
 
 int li_attention_generic(const void* qkv, void* out, const void* kcache, const void* vcache, int dtype, const int* block_table,
